@@ -1,4 +1,5 @@
 from .fields import read_config_dict, required, optional
+from .mabedra import MabedraConfig
 from .qwen3 import Qwen3Config
 from .ropulix import RopulixConfig
 from .sorulix import SorulixConfig
@@ -12,6 +13,7 @@ from .registry import (
 
 __all__ = [
     "Architecture",
+    "MabedraConfig",
     "Qwen3Config",
     "RopulixConfig",
     "SorulixConfig",

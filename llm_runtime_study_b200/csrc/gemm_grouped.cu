@@ -254,7 +254,7 @@ int launch_grouped_mma(const GroupedArgs& g, int batch, int act, cudaStream_t st
 template <typename T>
 __global__ void __launch_bounds__(128)
 route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ br, int* __restrict__ ids,
-             float* __restrict__ wts, int width, int experts, int top) {
+             float* __restrict__ wts, int width, int experts, int top, int score) {
   extern __shared__ float logits[];          // [experts], then [4][8] partial sums
   float* part = logits + experts;
   pdl_trigger();
@@ -297,7 +297,7 @@ route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float*
     __syncthreads();
   }
   if (warp != 0) return;
-  float first = 0.f, total = 0.f, mine = 0.f;
+  float first = 0.f, total = 0.f, mine = 0.f, mine_logit = 0.f;
   int my_id = 0;
   for (int j = 0; j < top; ++j) {
     float best = -INFINITY;
@@ -315,14 +315,15 @@ route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float*
     if (j == 0) first = best;
     const float p = expf(best - first);
     total += p;
-    if (lane == j) { mine = p; my_id = at; }
+    if (lane == j) { mine = p; mine_logit = best; my_id = at; }
     __syncwarp();
     if (lane == 0) logits[at] = -INFINITY;
     __syncwarp();
   }
   if (lane < top) {
     ids[static_cast<size_t>(token) * top + lane] = my_id;
-    wts[static_cast<size_t>(token) * top + lane] = mine / total;
+    // score 0: the softmax over the chosen logits; 1: each chosen logit's own sigmoid (the order of sigmoids is the logits')
+    wts[static_cast<size_t>(token) * top + lane] = score == 1 ? 1.f / (1.f + expf(-mine_logit)) : mine / total;
   }
 }
 
@@ -384,7 +385,7 @@ combine_kernel(const float* __restrict__ rows, const int* __restrict__ pair_row,
     float acc = 0.f;
     for (int j = 0; j < top; ++j) {
       const int p = token * top + j;
-      acc = fmaf(wts[p], rows[static_cast<size_t>(pair_row[p]) * width + c], acc);
+      acc = fmaf(wts ? wts[p] : 1.f, rows[static_cast<size_t>(pair_row[p]) * width + c], acc);
     }
     out[static_cast<size_t>(token) * width + c] = acc;
   }
@@ -443,13 +444,13 @@ extern "C" int b200_gemm_grouped(const void* A, long long lda, long long a_z, co
 }
 
 extern "C" int b200_moe_route(const void* h, const float* wr, const float* br, int* ids, float* wts, int n, int width, int experts,
-                              int top, int dtype, cudaStream_t stream) {
+                              int top, int score, int dtype, cudaStream_t stream) {
   using namespace b200;
   if (n <= 0) return 0;
   if (width <= 0 || experts <= 0 || top <= 0 || top > experts || top > 32 || experts > 2048) return B200_ERR_BAD_SIZE;
   const size_t smem = sizeof(float) * (experts + 32);
   B200_DISPATCH_DTYPE(dtype, T, launch(route_kernel<T>, dim3(n), dim3(128), smem, stream, static_cast<const T*>(h), wr, br,
-                                       ids, wts, width, experts, top));
+                                       ids, wts, width, experts, top, score));
   return launch_status();
 }
 

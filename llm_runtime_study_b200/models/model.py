@@ -56,7 +56,7 @@ class DecoderModel:
 
         needs = []
         for layer_index, source in zip(self.order, self.description.cache_of):
-            needs.append(None if source is not None else self.blocks[layer_index][1].mixer.cache_requirement())
+            needs.append(None if source is not None else self.blocks[layer_index][1].cache_requirement())
         return CacheLayout.from_requirements(needs)
 
     def bind_cache(self, manager: CacheManager) -> None:

@@ -78,10 +78,15 @@ def tile_rows() -> int:
     return query("b200_moe_tile_rows")
 
 
-def route(h: torch.Tensor, router: torch.Tensor, bias: torch.Tensor | None, *, top: int, wide_tiles: bool = False) -> Routing:
+SCORES = {"softmax_chosen": 0, "sigmoid": 1}
+
+
+def route(h: torch.Tensor, router: torch.Tensor, bias: torch.Tensor | None, *, top: int, wide_tiles: bool = False,
+          score: str = "softmax_chosen") -> Routing:
     """Logits ``router @ h + bias`` in float32 (``router`` float32 ``[experts, width]``; ``h`` in the activation type), the ``top``
-    largest chosen (the lower index wins a tie), weights the softmax over the chosen logits; then the pairs sorted by expert,
-    each expert's rows padded to whole tiles (of 128 rows with ``wide_tiles``, what the tcgen05 kernel takes; else of 64)."""
+    largest chosen (the lower index wins a tie); weights by ``score``: the softmax over the chosen logits, or each chosen
+    logit's sigmoid (not renormalised).  Then the pairs sorted by expert, each expert's rows padded to whole tiles (of 128
+    rows with ``wide_tiles``, what the tcgen05 kernel takes; else of 64)."""
 
     require(h, "h", dims=2)
     n, width = h.shape
@@ -94,7 +99,10 @@ def route(h: torch.Tensor, router: torch.Tensor, bias: torch.Tensor | None, *, t
     dev = h.device
     ids = torch.empty((n, top), dtype=torch.int32, device=dev)
     weights = torch.empty((n, top), dtype=torch.float32, device=dev)
-    call("b200_moe_route", ptr(h), ptr(router), ptr(bias), ptr(ids), ptr(weights), n, width, experts, top, tag(h.dtype), stream_ptr())
+    if score not in SCORES:
+        raise KernelError(f"unknown router score {score!r}; expected one of {sorted(SCORES)}")
+    call("b200_moe_route", ptr(h), ptr(router), ptr(bias), ptr(ids), ptr(weights), n, width, experts, top, SCORES[score], tag(h.dtype),
+         stream_ptr())
     tile = TC_TILE_ROWS if wide_tiles else tile_rows()
     max_tiles = min(-(-n * top // tile) + experts, n * top)       # a tile holds one expert's rows only
     pair_row = torch.empty(n * top, dtype=torch.int32, device=dev)
@@ -151,11 +159,13 @@ def expert_linear(a: torch.Tensor, weight: torch.Tensor, routing: Routing, *, ga
     return out
 
 
-def combine(rows: torch.Tensor, routing: Routing) -> torch.Tensor:
-    """``out[t] = sum_j weights[t, j] * rows[pair_row[t, j]]`` (float32, ``j`` ascending)."""
+def combine(rows: torch.Tensor, routing: Routing, *, weighted: bool = True) -> torch.Tensor:
+    """``out[t] = sum_j weights[t, j] * rows[pair_row[t, j]]`` (float32, ``j`` ascending); without ``weighted`` the plain sum
+    (the weights went into the experts' inputs)."""
 
     require(rows, "rows", dtype=torch.float32, dims=2)
     n = routing.ids.shape[0]
     out = torch.empty((n, rows.shape[1]), dtype=torch.float32, device=rows.device)
-    call("b200_moe_combine", ptr(rows), ptr(routing.pair_row), ptr(routing.weights), ptr(out), n, rows.shape[1], routing.top, stream_ptr())
+    call("b200_moe_combine", ptr(rows), ptr(routing.pair_row), ptr(routing.weights) if weighted else None, ptr(out), n, rows.shape[1],
+         routing.top, stream_ptr())
     return out

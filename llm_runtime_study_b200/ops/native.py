@@ -120,11 +120,34 @@ _LIBRARIES = {
             "b200_gemm_grouped": [c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_void_p, c_longlong, c_longlong, c_int,
                                   c_void_p, c_longlong, c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                   c_int, c_int, c_int, c_void_p],
-            "b200_moe_route": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+            "b200_moe_route": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
             "b200_moe_tile_rows": [],
             "b200_moe_plan": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
             "b200_gather_rows_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
             "b200_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        },
+    ),
+    "b200_block_steps": (
+        ("block_steps.cu",),
+        {
+            "b200_layer_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
+            "b200_taps_pair": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                               c_int, c_int, c_int, c_void_p],
+            "b200_scale_sum_average": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                       c_void_p],
+            "b200_poly_norm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
+            "b200_silu_mul_scaled": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        },
+    ),
+    "b200_attention_diff": (
+        ("attention_diff.cu",),
+        {
+            "b200_map_norm_rope_write": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p, c_void_p,
+                                         c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                         c_void_p],
+            "b200_diff_attention_simt": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                         c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_float, c_float, c_int, c_int,
+                                         c_void_p],
         },
     ),
 }

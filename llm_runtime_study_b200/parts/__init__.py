@@ -1,4 +1,4 @@
-from . import attention, block, experts, gated_attention, gated_recurrence, linear_state, mlp, norm, rope, stream_steps  # registers the built-in kinds
+from . import attention, block, differential_attention, experts, gated_attention, gated_recurrence, linear_state, mlp, norm, rope, stream_steps  # registers the built-in kinds
 from .base import (
     BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, Block, FeedForward, FixedState,
     Mixer, Norm, PagedKV, PagedTensors, Part, PositionEncoding, Registry, ResidualStream, Runtime, STREAM_STEPS, StreamStep,

@@ -195,6 +195,11 @@ class Block(Part):
 
         return None
 
+    def cache_requirement(self) -> "PagedTensors | FixedState | tuple | None":
+        """What the layer keeps per request: its mixer's needs, and whatever the block keeps itself."""
+
+        return self.mixer.cache_requirement()
+
     def forward(self, stream: "ResidualStream", ctx: Any, cache: Any) -> None:
         raise NotImplementedError
 
@@ -239,6 +244,7 @@ class ResidualStream:
     weighted: WeightedRows | None = None
     weighted_for: Any = None
     rounded: torch.Tensor | None = None     # the residual rows in the activation type, where the last block made that copy
+    results: torch.Tensor | None = None     # [layers + 1, rows, width]: every layer's result, for blocks that average over them
 
     def take_rows(self, norm: "Norm", consumer: Any) -> "torch.Tensor | WeightedRows":
         """What ``consumer`` gets as the rows normalised by ``norm``."""

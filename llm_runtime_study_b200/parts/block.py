@@ -139,3 +139,127 @@ class OutputNormBlock(Block):
             x = M.norm_accumulate_round(out, weight, eps, resid, act if rounds else None)
         if rounds:
             stream.rounded = x
+
+
+_PARALLEL_NAMES = {
+    "norm": "norm1", "mixer": "mix", "feed_forward": "mlp", "mixer_scale": "ls1", "ffn_scale": "ls2",
+    "mixer_taps": "canon1", "ffn_taps": "canon2", "average": "dwa",
+}
+
+
+@BLOCKS.register("parallel_sublayers")
+class ParallelSublayersBlock(Block):
+    """One norm, both sublayers read its output: with ``h = norm(x)``,
+    ``x_new = x + s1 * mixer(h + conv1(h)) + s2 * ff(h + conv2(h))``.
+
+    * ``taps`` > 1: each sublayer's input is ``h + conv(h)``, a causal convolution over time per channel with weights
+      ``[width, taps]`` of its own (``conv(h)_t = sum_j w[:, j] h_(t - taps + 1 + j)``, zeros before the sequence's start).  The
+      last ``taps - 1`` rows of ``h`` are kept per request (float32), one array for both sublayers since they read the same ``h``.
+    * ``layer_scale``: ``s1`` and ``s2`` are vectors of the width (otherwise 1).
+    * ``average_over = k``: the block's result is kept beside the results of all blocks before it and the embedding's
+      output (``k`` rows of the stream in all), and the stream handed on is ``sum_j a[j] * result_j`` with the block's
+      own ``k`` weights.  ``None``: the stream is the block's result.  ``average_capacity``: the largest ``k`` among the model's
+      blocks (room for all results is made once per step, by the first block).
+
+    The norm's output, the convolution's sums and the stream stay float32; the sublayers get their inputs in the run type.
+    ``names`` gives the checkpoint's name of each sub-part below the layer's prefix."""
+
+    graph_safe = True
+    KEPT = "kept_inputs"
+
+    def __init__(
+        self, *, hidden_size: int, mixer: Mapping[str, Any], feed_forward: Mapping[str, Any] | None, norm: Mapping[str, Any],
+        taps: int = 1, layer_scale: bool = False, average_over: int | None = None, average_capacity: int | None = None,
+        names: Mapping[str, str] | None = None,
+    ) -> None:
+        if hidden_size <= 0 or taps <= 0 or (average_over is not None and average_over < 2):
+            raise ValueError("a parallel_sublayers block needs a positive width and taps, and an average over at least two results")
+        self.names = {**_PARALLEL_NAMES, **(names or {})}
+        self.hidden_size, self.taps, self.layer_scale, self.average_over = hidden_size, int(taps), bool(layer_scale), average_over
+        # how many results the model's deepest block of this kind averages over: room for them is made once per step
+        self.average_capacity = max(average_capacity or 0, average_over or 0)
+        self.norm = NORMS.build(norm)
+        self.mixer = MIXERS.build(mixer)
+        self.feed_forward = FEED_FORWARDS.build(feed_forward) if feed_forward else None
+
+    def children(self):
+        return tuple(part for _, part in self._parts())
+
+    def _parts(self):
+        parts = [(self.names["norm"], self.norm), (self.names["mixer"], self.mixer)]
+        if self.feed_forward is not None:
+            parts.append((self.names["feed_forward"], self.feed_forward))
+        return tuple(parts)
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        specs = {f"{prefix}.{n}": s for prefix, part in self._parts() for n, s in part.tensor_specs().items()}
+        w, ff = self.hidden_size, self.feed_forward is not None
+        if self.layer_scale:
+            specs[self.names["mixer_scale"]] = TensorSpec((w,), init="one_plus_normal", std=0.2)
+            if ff:
+                specs[self.names["ffn_scale"]] = TensorSpec((w,), init="one_plus_normal", std=0.2)
+        if self.taps > 1:
+            specs[self.names["mixer_taps"]] = TensorSpec((w, self.taps), init="normal", std=0.3)
+            if ff:
+                specs[self.names["ffn_taps"]] = TensorSpec((w, self.taps), init="normal", std=0.3)
+        if self.average_over is not None:
+            specs[self.names["average"]] = TensorSpec((self.average_over,), init="normal", std=0.6)
+        return specs
+
+    def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
+        self.runtime = runtime
+        view = TensorView.of(tensors)
+        for prefix, part in self._parts():
+            part.load(view.sub(prefix), runtime)
+        ff = self.feed_forward is not None
+        f32 = runtime.place_vector_f32
+        self.mixer_scale = f32(tensors[self.names["mixer_scale"]]) if self.layer_scale else None
+        self.ffn_scale = f32(tensors[self.names["ffn_scale"]]) if self.layer_scale and ff else None
+        self.mixer_taps = f32(tensors[self.names["mixer_taps"]]) if self.taps > 1 else None
+        self.ffn_taps = f32(tensors[self.names["ffn_taps"]]) if self.taps > 1 and ff else None
+        self.average = f32(tensors[self.names["average"]]) if self.average_over is not None else None
+
+    def first_norm(self):
+        return self.norm
+
+    def cache_requirement(self):
+        needs = self.mixer.cache_requirement()
+        needs = () if needs is None else (tuple(needs) if isinstance(needs, (tuple, list)) else (needs,))
+        if self.taps > 1:
+            from .base import FixedState
+
+            needs += (FixedState((self.taps - 1, self.hidden_size), torch.float32, name=self.KEPT),)
+        return needs or None
+
+    def forward(self, stream: ResidualStream, ctx: Any, cache: Any) -> None:
+        from ..ops import block_steps as B
+        from ..ops import sequence_state as S
+
+        resid, act = stream.resid, self.runtime.dtype
+        delta = stream.delta
+        stream.put(None, None)
+        if self.average_over is not None and stream.results is None:
+            # the first block of this kind: the rows it starts from are result 0 (the embedding's output)
+            if delta is not None:
+                resid += delta
+                delta = None
+            stream.results = torch.empty((self.average_capacity, *resid.shape), dtype=torch.float32, device=resid.device)
+            stream.results[0].copy_(resid)
+        if self.taps > 1:
+            h = self.norm.add_norm(resid, delta, torch.float32)
+            kept = cache.states[self.KEPT]
+            x_mix, x_ff = B.taps_pair(h, self.mixer_taps, self.ffn_taps, kept, q_start=ctx.q_start, slots=ctx.slots,
+                                      token_entry=ctx.token_entry, out_dtype=act)
+            S.conv_state_update(h, kept, ctx.q_start, ctx.slots)
+        else:
+            x_mix = x_ff = self.norm.add_norm(resid, delta)
+        out_mix = self.mixer.forward(x_mix, ctx, cache)
+        out_ff = self.feed_forward.forward(x_ff, ctx) if self.feed_forward is not None else None
+        results = stream.results
+        if self.average_over is not None and results.shape[0] < self.average_over:
+            # blocks further down average over more results than the first one made room for
+            grown = torch.empty((self.average_over, *resid.shape), dtype=torch.float32, device=resid.device)
+            grown[: results.shape[0]].copy_(results)
+            results = stream.results = grown
+        B.scale_sum_average(resid, out_mix, self.mixer_scale, out_ff, self.ffn_scale, results, self.average,
+                            (self.average_over or 2) - 2)

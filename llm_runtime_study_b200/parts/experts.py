@@ -6,32 +6,54 @@ from typing import Any, Mapping
 
 import torch
 
+from ..ops import block_steps as B
 from ..ops import grouped as G
 from ..ops.mixer_steps import PairedRows
 from ..weights.checkpoint import TensorSpec
 from .base import FEED_FORWARDS, FeedForward, Runtime
+from .linear import Projection
+
+ACTS = ("relu2", "silu_glu")
 
 
 @FEED_FORWARDS.register("routed_experts")
 class RoutedExperts(FeedForward):
-    """``experts`` feed-forward layers ``W_down act(W_up x)`` without biases (``act``: ``relu2``, the square of relu).  Router
-    logits ``z = W_router x + b_router`` in float32; each token uses the ``top`` experts with the largest logits, weighted by
-    the softmax over the chosen logits only; the output is the weighted sum.  Tensors: ``router``, ``router.b``,
-    ``e<j>.up`` ``[ff, hidden]``, ``e<j>.down`` ``[hidden, ff]``.
+    """``experts`` feed-forward layers without biases, of which each token uses the ``top`` with the largest router logits
+    ``z = W_router x (+ b_router)`` (float32).  Every choice is a parameter:
+
+    * ``act``: ``relu2``: an expert is ``W_down relu(W_up x)^2``; ``silu_glu``: ``W_down (silu(W_gate x) * (W_up x))``.
+    * ``score``: ``softmax_chosen``: the weights are the softmax over the chosen logits only; ``sigmoid``: each chosen
+      expert's ``sigmoid(z)``, not renormalised.
+    * ``weight_on``: ``output``: the result is ``sum w_e expert_e(x)``; ``input``: ``sum expert_e(w_e x)``.
+    * ``shared_size``: a further expert of that inner size (same form) that runs for every token and is added.
+
+    Tensors: ``router`` (``router.b``), ``e<j>.up`` ``[ff, hidden]`` (``e<j>.gate``), ``e<j>.down`` ``[hidden, ff]``,
+    ``shared.gate|up|down``.
 
     The (token, choice) pairs are sorted by expert on the device and every expert's rows are padded to whole tiles, so the
-    two products run as one launch each over all experts, sized without the host knowing the counts."""
+    two products run as one launch each over all experts, sized without the host knowing the counts.  With ``input`` weights
+    the factor is applied where the gated unit is formed: ``W (w x) = w (W x)``, so ``silu(w g) * (w u)`` of the unweighted
+    products ``g`` and ``u`` is the same expert on the weighted input."""
 
     graph_safe = True
 
     def __init__(self, *, hidden_size: int, intermediate_size: int, experts: int, top: int, act: str = "relu2",
-                 router_bias: bool = True) -> None:
+                 router_bias: bool = True, score: str = "softmax_chosen", weight_on: str = "output",
+                 shared_size: int | None = None) -> None:
         if min(hidden_size, intermediate_size, experts, top) <= 0 or top > experts:
             raise ValueError("expert sizes must be positive and top at most the number of experts")
-        if act != "relu2":
-            raise ValueError(f"unknown expert activation {act!r}; expected relu2")
+        if act not in ACTS:
+            raise ValueError(f"unknown expert activation {act!r}; expected one of {ACTS}")
+        if score not in G.SCORES:
+            raise ValueError(f"unknown router score {score!r}; expected one of {sorted(G.SCORES)}")
+        if weight_on not in ("output", "input"):
+            raise ValueError(f"weight_on is 'output' or 'input', got {weight_on!r}")
+        if weight_on == "input" and act != "silu_glu":
+            raise ValueError("weights on the experts' inputs are built for the gated unit only")
+        if shared_size is not None and (shared_size <= 0 or act != "silu_glu"):
+            raise ValueError("a shared expert needs a positive size and the gated unit")
         self.hidden_size, self.intermediate_size, self.experts, self.top = hidden_size, intermediate_size, experts, top
-        self.act, self.router_bias = act, bool(router_bias)
+        self.act, self.router_bias, self.score, self.weight_on, self.shared_size = act, bool(router_bias), score, weight_on, shared_size
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
         h, f = self.hidden_size, self.intermediate_size
@@ -39,28 +61,54 @@ class RoutedExperts(FeedForward):
         if self.router_bias:
             specs["router.b"] = TensorSpec((self.experts,), init="normal", std=0.5)
         for e in range(self.experts):
+            if self.act == "silu_glu":
+                specs[f"e{e}.gate"] = TensorSpec((f, h))
             specs[f"e{e}.up"] = TensorSpec((f, h))
             specs[f"e{e}.down"] = TensorSpec((h, f))
+        if self.shared_size is not None:
+            specs.update({"shared.gate": TensorSpec((self.shared_size, h)), "shared.up": TensorSpec((self.shared_size, h)),
+                          "shared.down": TensorSpec((h, self.shared_size))})
         return specs
 
     def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
         self.runtime = runtime
         self.router = tensors["router"].to(device=runtime.device).to(torch.float32).contiguous()
         self.router_b = runtime.place_vector_f32(tensors["router.b"]) if self.router_bias else None
-        self.up = torch.stack([runtime.place_matrix(tensors[f"e{e}.up"]) for e in range(self.experts)])
+        if self.act == "silu_glu":      # per expert: the rows of gate, then the rows of up (one product gives both)
+            self.up = torch.stack([torch.cat([runtime.place_matrix(tensors[f"e{e}.gate"]), runtime.place_matrix(tensors[f"e{e}.up"])])
+                                   for e in range(self.experts)])
+        else:
+            self.up = torch.stack([runtime.place_matrix(tensors[f"e{e}.up"]) for e in range(self.experts)])
         self.down = torch.stack([runtime.place_matrix(tensors[f"e{e}.down"]) for e in range(self.experts)])
+        self.shared_up = self.shared_down = None
+        if self.shared_size is not None:
+            self.shared_up = Projection([tensors["shared.gate"], tensors["shared.up"]], None, runtime)
+            self.shared_down = Projection([tensors["shared.down"]], None, runtime)
 
     # the weighted sum over a token's experts may be left to the consumer (``PairedRows``): see ``forward``
-    returns_pieces = True
+    @property
+    def returns_pieces(self) -> bool:
+        return self.shared_size is None and self.weight_on == "output"
 
     def forward(self, x: torch.Tensor, ctx: Any, *, pieces: bool = False) -> "torch.Tensor | PairedRows":
         """``pieces``: return the experts' rows with the pairing instead of their weighted sum, for a consumer that forms the
         sum while it reads the rows anyway (the norm behind this part does)."""
 
         wide = G.wide_tiles_pay(x.shape[0], self.top, x.dtype, self.hidden_size, self.intermediate_size)
-        routing = G.route(x, self.router, self.router_b, top=self.top, wide_tiles=wide)
-        hidden = G.expert_linear(x, self.up, routing, gather=True, act=self.act)
+        routing = G.route(x, self.router, self.router_b, top=self.top, wide_tiles=wide, score=self.score)
+        if self.act == "silu_glu":
+            gate_up = G.expert_linear(x, self.up, routing, gather=True)
+            on_input = self.weight_on == "input"
+            hidden = B.silu_mul_scaled(gate_up, routing.pair_row, routing.weights.view(-1) if on_input else None)
+        else:
+            on_input = False
+            hidden = G.expert_linear(x, self.up, routing, gather=True, act=self.act)
         rows = G.expert_linear(hidden, self.down, routing, gather=False, out_dtype=torch.float32)
-        if pieces:
+        if pieces and self.returns_pieces:
             return PairedRows(rows, routing.pair_row, routing.weights)
-        return G.combine(rows, routing)
+        out = G.combine(rows, routing, weighted=not on_input)
+        if self.shared_down is not None:
+            shared = self.shared_down(B.silu_mul_scaled(self.shared_up(x)), torch.float32, add_to=out)
+            if shared is not None:
+                out += shared
+        return out

@@ -6,6 +6,7 @@ from typing import Any, Mapping
 
 import torch
 
+from ..ops import block_steps as B
 from ..ops import functional as F
 from ..weights.checkpoint import TensorSpec
 from .base import FEED_FORWARDS, FeedForward, Runtime
@@ -88,3 +89,30 @@ class LimitedGLU(FeedForward):
     def forward(self, x: Any, ctx: Any, residual: torch.Tensor | None = None):
         hidden = F.glu_limit(self.gate_up_proj(x), self.limit, self.alpha)
         return self.down_proj(hidden, torch.float32, add_to=residual)
+
+
+@FEED_FORWARDS.register("poly_norm_mlp")
+class PolyNormMLP(FeedForward):
+    """``W_down act(W_up x)`` without biases, ``act(z) = a u(z) + b u(z^2) + c u(z^3) + e`` with element-wise powers and
+    ``u(y) = y / sqrt(mean(y^2) + eps)`` over a token's ``intermediate_size`` values (statistics in float32).  Tensors:
+    ``up``, ``down``, ``act`` (the four numbers a, b, c, e)."""
+
+    graph_safe = True
+
+    def __init__(self, *, hidden_size: int, intermediate_size: int, eps: float) -> None:
+        if hidden_size <= 0 or intermediate_size <= 0 or eps <= 0:
+            raise ValueError("poly_norm_mlp sizes and eps must be positive")
+        self.hidden_size, self.intermediate_size, self.eps = hidden_size, intermediate_size, float(eps)
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        h, i = self.hidden_size, self.intermediate_size
+        return {"up": TensorSpec((i, h)), "down": TensorSpec((h, i)), "act": TensorSpec((4,), init="normal", std=0.5)}
+
+    def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
+        self.runtime = runtime
+        self.up_proj = Projection([tensors["up"]], None, runtime)
+        self.down_proj = Projection([tensors["down"]], None, runtime)
+        self.coef = runtime.place_vector_f32(tensors["act"])
+
+    def forward(self, x: Any, ctx: Any) -> torch.Tensor:
+        return self.down_proj(B.poly_norm(self.up_proj(x), self.coef, self.eps), torch.float32)
