@@ -360,3 +360,78 @@ def make_ropulix_dir(path: Path, config: dict, seed: int, *, torch_dtype: str = 
     (path / "config.json").write_text(json.dumps(config, indent=1), encoding="utf-8")
     write_file(path / "model.safetensors", state)
     return path, state
+
+
+# ----------------------------------------------------------------- Mabedra
+# A: sizes that are no multiples of 16, grouped heads sharing one key/value head, value sizes larger and smaller than the
+# key size, a rotation over part of a map and over all of it, stretched wavelengths of which some are kept, some blended
+# and some divided, a layer without a window, one without a rotation, one without a feed-forward, a dense feed-forward,
+# experts of which two of five or all three are used, with and without a shared expert, three taps.
+MABEDRA_A = {
+    "architecture": "Mabedra", "vocab": 157, "width": 48, "norm": {"eps": 1e-5}, "canon": {"taps": 3},
+    "layers": [
+        {"type": "attention", "mixer": {"heads": 3, "kv_heads": 1, "dim": 8, "vdim": 12, "diff": 0.2, "scale": 0.4, "mask": {"size": 7},
+                                        "rot": {"base": 500.0, "dims": 4, "scaling": {"factor": 4.0, "low": 1.0, "high": 3.0, "original": 32}}},
+         "mlp": {"kind": "dense", "ff": 40}},
+        {"type": "attention", "mixer": {"heads": 2, "kv_heads": 2, "dim": 16, "vdim": 8, "diff": 0.35, "scale": 0.25,
+                                        "rot": {"base": 100.0, "dims": 16, "scaling": {"factor": 2.0, "low": 1.0, "high": 4.0, "original": 64}}},
+         "mlp": {"kind": "moe", "expert": {"ff": 24}, "router": {"experts": 5, "top": 2}, "shared": {"ff": 16}}},
+        {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 8, "vdim": 8, "diff": 0.5, "scale": 0.35, "mask": {"size": 5}},
+         "mlp": None},
+        {"type": "attention", "mixer": {"heads": 1, "kv_heads": 1, "dim": 24, "vdim": 40, "diff": 0.1, "scale": 0.2, "mask": {"size": 33},
+                                        "rot": {"base": 10000.0, "dims": 24}},
+         "mlp": {"kind": "moe", "expert": {"ff": 16}, "router": {"experts": 3, "top": 3}}},
+    ],
+}
+# B: two taps, one expert of six used, as many key/value heads as query heads, a window of one page.
+MABEDRA_B = {
+    "architecture": "Mabedra", "vocab": 131, "width": 64, "norm": {"eps": 1e-6}, "canon": {"taps": 2},
+    "layers": [
+        {"type": "attention", "mixer": {"heads": 2, "kv_heads": 1, "dim": 32, "vdim": 16, "diff": 0.25, "scale": 0.18, "mask": {"size": 16},
+                                        "rot": {"base": 3000.0, "dims": 32, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 128}}},
+         "mlp": {"kind": "dense", "ff": 72}},
+        {"type": "attention", "mixer": {"heads": 4, "kv_heads": 4, "dim": 16, "vdim": 16, "diff": 0.4, "scale": 0.25, "mask": {"size": 40},
+                                        "rot": {"base": 3000.0, "dims": 8}},
+         "mlp": {"kind": "moe", "expert": {"ff": 32}, "router": {"experts": 6, "top": 1}, "shared": {"ff": 48}}},
+    ],
+}
+# C: sizes in steps of 16 throughout (what the tensor-core kernels of the bfloat16 run type take), no convolution on the
+# sublayers' inputs, windows of 24 and 50 and none, heads of 32 with values of 64 and heads of 64 with values of 32.
+MABEDRA_C = {
+    "architecture": "Mabedra", "vocab": 151, "width": 128, "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 64, "diff": 0.3, "scale": 0.18, "mask": {"size": 24},
+                                        "rot": {"base": 5000.0, "dims": 32}},
+         "mlp": {"kind": "moe", "expert": {"ff": 64}, "router": {"experts": 6, "top": 2}, "shared": {"ff": 32}}},
+        {"type": "attention", "mixer": {"heads": 2, "kv_heads": 1, "dim": 64, "vdim": 32, "diff": 0.15, "scale": 0.125, "mask": {"size": 50},
+                                        "rot": {"base": 5000.0, "dims": 16}},
+         "mlp": {"kind": "dense", "ff": 192}},
+        {"type": "attention", "mixer": {"heads": 2, "kv_heads": 2, "dim": 48, "vdim": 48, "diff": 0.3, "scale": 0.14,
+                                        "rot": {"base": 20000.0, "dims": 48, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 256}}},
+         "mlp": {"kind": "moe", "expert": {"ff": 64}, "router": {"experts": 6, "top": 2}, "shared": {"ff": 32}}},
+    ],
+}
+MABEDRA = {"A": (MABEDRA_A, 31, 4), "B": (MABEDRA_B, 32, 16), "C": (MABEDRA_C, 33, 16)}   # config, seed, page size
+
+
+def make_mabedra_dir(path: Path, config: dict, seed: int, *, torch_dtype: str = "float32", gain: float = 6.0):
+    """Write a Mabedra model folder with random weights; return (path, {name: CPU tensor as stored}).  The matrices are
+    drawn ``gain`` times larger than the framework's default, so that scores and routers are not all alike."""
+
+    from llm_runtime_study_b200.config import MabedraConfig
+    from llm_runtime_study_b200.models.description import tensor_schema
+    from llm_runtime_study_b200.models.mabedra import describe_mabedra
+    from llm_runtime_study_b200.weights.random_init import random_state
+    from llm_runtime_study_b200.weights.safetensors_io import write_file
+
+    schema = tensor_schema(describe_mabedra(MabedraConfig.from_dict(config)))
+    dtype = {"float32": torch.float32, "bfloat16": torch.bfloat16}[torch_dtype]
+    state = random_state(schema, seed, dtype=torch.float32, include_optional=False)
+    for name, tensor in state.items():
+        if tensor.dim() == 2 and not name.endswith((".canon1", ".canon2", ".router")):
+            tensor *= gain
+    state = {name: tensor.to(dtype) for name, tensor in state.items()}
+    path.mkdir(parents=True, exist_ok=True)
+    (path / "config.json").write_text(json.dumps(config, indent=1), encoding="utf-8")
+    write_file(path / "model.safetensors", state)
+    return path, state

@@ -155,13 +155,18 @@ def gated_expert(h, W, prefix: str, store=keep) -> torch.Tensor:
     return store(silu(store(h @ W[prefix + "gate"].T)) * store(h @ W[prefix + "up"].T)) @ W[prefix + "down"].T
 
 
-def routed_ff(h, W, mlp: Mapping, store=keep) -> torch.Tensor:
+def routed_ff(h, W, mlp: Mapping, store=keep, margins=None) -> torch.Tensor:
     """Sigmoid scores, the ``top`` largest chosen, the score multiplies the chosen expert's *input*; a shared expert
-    runs for every token."""
+    runs for every token.  ``margins`` (a list) receives, per token, the gap between the last chosen logit and the first
+    one left out (infinite when every expert is used)."""
 
     experts, top = int(mlp["router"]["experts"]), int(mlp["router"]["top"])
-    scores = sigmoid(h @ W["router"].T)
-    chosen = torch.topk(scores, top, dim=-1).indices
+    logits = h @ W["router"].T
+    scores = sigmoid(logits)
+    chosen = torch.topk(logits, top, dim=-1).indices          # the sigmoid keeps the order of the logits
+    if margins is not None:
+        ordered = torch.sort(logits, dim=-1, descending=True).values
+        margins.append(ordered[:, top - 1] - ordered[:, top] if top < experts else torch.full((h.shape[0],), math.inf, dtype=h.dtype))
     out = torch.zeros(h.shape[0], W["e0.down"].shape[0], dtype=h.dtype)
     for t in range(h.shape[0]):
         for e in chosen[t].tolist():
@@ -176,8 +181,8 @@ def sub(weights: Mapping[str, torch.Tensor], prefix: str, dtype) -> dict:
     return {n[len(prefix):]: t.to(dtype) for n, t in weights.items() if n.startswith(prefix)}
 
 
-def forward(config: Mapping, weights: Mapping[str, torch.Tensor], tokens, dtype=torch.float64, store=keep, layers_out=None):
-    """Logits ``[T, vocab]``.  ``layers_out`` (a list) receives the stream after every layer."""
+def forward(config: Mapping, weights: Mapping[str, torch.Tensor], tokens, dtype=torch.float64, store=keep, layers_out=None, margins=None):
+    """Logits ``[T, vocab]``.  ``layers_out`` (a list) receives the stream after every layer, ``margins`` every router's."""
 
     eps = float(config["norm"]["eps"])
     x = weights["embed"].to(dtype)[torch.as_tensor(tokens, dtype=torch.long)]
@@ -191,7 +196,7 @@ def forward(config: Mapping, weights: Mapping[str, torch.Tensor], tokens, dtype=
         if mlp:
             h_ff = store(h + causal_taps(h, L["canon2"])) if "canon2" in L else store(h)
             M = sub(L, "mlp.", dtype)
-            ff = dense_ff(h_ff, M, eps, store) if mlp["kind"] == "dense" else routed_ff(h_ff, M, mlp, store)
+            ff = dense_ff(h_ff, M, eps, store) if mlp["kind"] == "dense" else routed_ff(h_ff, M, mlp, store, margins)
             new = new + L["ls2"] * ff
         history.append(new)
         x = sum(L["dwa"][j] * history[j] for j in range(i + 2))
