@@ -2,10 +2,48 @@
 
 from __future__ import annotations
 
+import ctypes
+import os
+from typing import Any
+
 import torch
 
 from ..errors import KernelError
-from .native import call, ptr, require, stream_ptr, tag
+from . import native
+from .native import c_float, c_int, c_void_p, call, ptr, require, stream_ptr, tag
+
+# "mma": the tensor-core kernel wherever it takes the sizes; "simt": the CUDA-core kernel everywhere
+BACKEND = os.environ.get("LLM_RUNTIME_STUDY_B200_ATTENTION_DIFF", "mma")
+ROWS_PER_TILE = 64
+
+_TABLE = {
+    "b200_attention_diff_dim": [],
+    "b200_attention_diff_vdim": [],
+    "b200_attention_diff_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int,
+                                 c_float, c_float, c_float, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, ctypes.c_long,
+                                 c_void_p],
+}
+_SOURCES = ("attention_diff_mma.cu",)
+
+
+def library_name(head_dim: int, value_dim: int) -> str:
+    name = f"b200_attention_diff_d{head_dim}_v{value_dim}"
+    if name not in native.library_specs():
+        native.register_library(name, _SOURCES, _TABLE, defines=(f"DIFF_DIM={head_dim}", f"DIFF_VDIM={value_dim}"))
+    return name
+
+
+def supported(head_dim: int, value_dim: int) -> bool:
+    """Both widths in steps of 16 up to 256: what the tensor-core kernel is built for."""
+
+    return head_dim % 16 == 0 and value_dim % 16 == 0 and 16 <= head_dim <= 256 and 16 <= value_dim <= 256
+
+
+def build(head_dim: int, value_dim: int) -> None:
+    from ..csrc.build import build_library
+
+    name = library_name(head_dim, value_dim)
+    build_library(name, _SOURCES, native.library_defines(name))
 
 
 def map_norm_rope_write(
@@ -72,9 +110,68 @@ def diff_attention_simt(
     return out
 
 
+def diff_attention_mma(
+    q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx: Any, table: torch.Tensor, *, scale: float, window: int, lam: float,
+    out_scale: float, eps: float, normalise: bool = True, splits: int | None = None,
+) -> torch.Tensor:
+    """The same on tensor cores (bfloat16, both widths in steps of 16): prompt portions and single tokens alike; a tile is up
+    to ``64 // min(64, nq // nkv)`` consecutive tokens of one request times the query heads of one key/value head.  A batch of
+    single tokens has every token's keys cut into ``splits`` parts (``None``: chosen from the batch), merged by a second launch."""
+
+    require(q, "q", dtype=torch.bfloat16, dims=3)
+    n, nq, two_d = q.shape
+    require(k_pool, "k_pool", dtype=q.dtype, dims=4)
+    require(v_pool, "v_pool", dtype=q.dtype, dims=4)
+    _, nkv, page_size, kd = k_pool.shape
+    d, dv = two_d // 2, v_pool.shape[3]
+    if kd != two_d or two_d % 2 or tuple(v_pool.shape[:3]) != tuple(k_pool.shape[:3]) or nq % nkv:
+        raise KernelError(f"q {tuple(q.shape)}, key pool {tuple(k_pool.shape)} and value pool {tuple(v_pool.shape)} do not fit")
+    if not supported(d, dv):
+        raise KernelError(f"the tensor-core kernel takes widths in steps of 16 up to 256, not {d} and {dv}")
+    group_heads = min(nq // nkv, ROWS_PER_TILE)
+    slices = -(-(nq // nkv) // group_heads)
+    per_tile = max(1, ROWS_PER_TILE // group_heads)
+    decode = ctx.all_decode and n == ctx.num_entries
+    maps = ctx.__dict__.setdefault("_tile_maps", {})
+    key = ("diff", per_tile)
+    if key not in maps:
+        from . import attention_bf16, attention_latent
+
+        if decode:
+            maps[key] = (attention_latent._single_token_tiles(n, q.device), n)      # one tile a request
+        else:
+            maps[key] = attention_bf16.tile_map(ctx.q_lens, per_tile, q.device, ctx.kv_lens)
+    tiles, count = maps[key]
+    out = torch.empty((n, nq, dv), dtype=q.dtype, device=q.device)
+    scratch, floats = None, 0
+    if not decode:
+        splits = 1
+    elif splits is None:
+        splits = decode_splits(n * nkv * slices, min(window, ctx.max_kv_len) if window else ctx.max_kv_len)
+    if splits > 1:
+        floats = n * nq * 2 * splits * (dv + 2)
+        scratch = torch.empty(floats, dtype=torch.float32, device=q.device)
+    native.call("b200_attention_diff_bf16", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(), ctx.positions.data_ptr(),
+                table.data_ptr(), table.shape[1], page_size, nq, nkv, float(scale), int(window), float(lam), float(out_scale), float(eps),
+                1 if normalise else 0, tiles[0].data_ptr(), tiles[1].data_ptr(), tiles[2].data_ptr(), count, splits, ptr(scratch), floats,
+                stream_ptr(), library=library_name(d, dv), launches=2 if splits > 1 else 1)
+    return out
+
+
+def decode_splits(ctas: int, keys: int) -> int:
+    """Into how many parts a single token's keys are cut: enough CTAs for two a multiprocessor, no part shorter than four
+    tiles of 32 keys, at most 32 parts."""
+
+    wanted = -(-2 * native.sm_count() // max(ctas, 1))
+    return max(1, min(wanted, keys // 128, 32))
+
+
 def diff_attention(q: torch.Tensor, cache, ctx, table: torch.Tensor, *, scale: float, window: int, lam: float, out_scale: float,
                    eps: float) -> torch.Tensor:
-    """The differential attention of the batch's query tokens over their requests' pages; chooses the kernel."""
+    """The differential attention of the batch's query tokens over their requests' pages; chooses the kernel: bfloat16 with
+    both widths in steps of 16 runs on tensor cores, float32 and every other size on CUDA cores in 32-bit arithmetic."""
 
+    if BACKEND == "mma" and q.dtype == torch.bfloat16 and supported(q.shape[2] // 2, cache.values.shape[3]):
+        return diff_attention_mma(q, cache.keys, cache.values, ctx, table, scale=scale, window=window, lam=lam, out_scale=out_scale, eps=eps)
     return diff_attention_simt(q, cache.keys, cache.values, positions=ctx.positions, token_entry=ctx.token_entry, block_table=table,
                                scale=scale, window=window, lam=lam, out_scale=out_scale, eps=eps)

@@ -109,6 +109,29 @@ def one_map(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, see
     return torch.softmax(s, dim=-1) @ v
 
 
+def differential_read_out(q, k, v, *, scale: float, window: int | None, lam: float, out_scale: float, eps: float,
+                          normalise: bool = True) -> torch.Tensor:
+    """``q`` ``[T, H, 2, d]``, ``k`` ``[T, G, 2, d]``, ``v`` ``[T, G, dv]`` at positions ``0..T-1``: per head
+    ``o = softmax(S_1) v - lam * softmax(S_2) v`` with ``S_m = scale * q_m k_m^T`` under the causal mask and the window,
+    then ``unit(o) * out_scale``.  Result ``[T, H, dv]``."""
+
+    T, H = q.shape[0], q.shape[1]
+    G = k.shape[1]
+    seen = window_mask(T, window)
+    out = torch.zeros(T, H, v.shape[2], dtype=q.dtype)
+    for head in range(H):
+        g = head // (H // G)
+        a1 = one_map(q[:, head, 0], k[:, g, 0], v[:, g], scale, seen)
+        a2 = one_map(q[:, head, 1], k[:, g, 1], v[:, g], scale, seen)
+        o = a1 - lam * a2
+        out[:, head] = (unit(o, eps) if normalise else o) * out_scale
+    return out
+
+
+def lambda_of(W, diff: float) -> torch.Tensor:
+    return torch.exp((W["lq1"] * W["lk1"]).sum()) - torch.exp((W["lq2"] * W["lk2"]).sum()) + diff
+
+
 def differential_attention(h, W, m: Mapping, eps: float, store=keep) -> torch.Tensor:
     """Two softmax maps per head over the same values, the second subtracted ``lambda`` times; the difference divided by
     its root mean square per head and scaled by ``1 - diff``."""
@@ -129,14 +152,8 @@ def differential_attention(h, W, m: Mapping, eps: float, store=keep) -> torch.Te
         q, k = rotate(q, positions, freqs), rotate(k, positions, freqs)
     q, k = store(q), store(k)
     mask = m.get("mask")
-    seen = window_mask(T, int(mask["size"]) if mask and mask.get("size") else None)
-    lam = torch.exp((W["lq1"] * W["lk1"]).sum()) - torch.exp((W["lq2"] * W["lk2"]).sum()) + diff
-    out = torch.zeros(T, H, dv, dtype=h.dtype)
-    for head in range(H):
-        g = head // (H // G)
-        a1 = one_map(q[:, head, 0], k[:, g, 0], v[:, g], float(m["scale"]), seen)
-        a2 = one_map(q[:, head, 1], k[:, g, 1], v[:, g], float(m["scale"]), seen)
-        out[:, head] = unit(a1 - lam * a2, eps) * (1.0 - diff)
+    out = differential_read_out(q, k, v, scale=float(m["scale"]), window=int(mask["size"]) if mask and mask.get("size") else None,
+                                lam=float(lambda_of(W, diff)), out_scale=1.0 - diff, eps=eps)
     return store(out).reshape(T, H * dv) @ W["o"].T
 
 
