@@ -915,6 +915,182 @@ def _ropulix_kernels(peak, timed) -> dict:
     return out
 
 
+# ------------------------------------------------------------------------------ Mabedra beside Ropulix and Qwen3
+MABEDRA_EXPERTS, MABEDRA_TOP, MABEDRA_WINDOW, MABEDRA_TAPS = 8, 2, 1024, 4
+
+
+def _mabedra_config(width, ff, heads, kv_heads, d, pairs, vocab) -> dict:
+    """Half as many heads as the plain attention of equal size, each with two maps of ``d`` columns and values of ``2 d``
+    (projections and cache rows of equal size); a dense layer whose two matrices hold what the gated unit's three do, then a
+    layer of experts: every token uses MABEDRA_TOP of ``ff / 4`` beside a shared one of ``ff / 2``."""
+
+    mixer = {"heads": heads // 2, "kv_heads": kv_heads // 2, "dim": d, "vdim": 2 * d, "diff": 0.3, "scale": d ** -0.5,
+             "mask": {"size": MABEDRA_WINDOW},
+             "rot": {"base": 10000.0, "dims": d, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    dense = {"kind": "dense", "ff": ff * 3 // 2}
+    moe = {"kind": "moe", "expert": {"ff": ff // 4}, "router": {"experts": MABEDRA_EXPERTS, "top": MABEDRA_TOP}, "shared": {"ff": ff // 2}}
+    layers = [{"type": "attention", "mixer": dict(mixer), "mlp": dense}, {"type": "attention", "mixer": dict(mixer), "mlp": moe}] * pairs
+    return {"architecture": "Mabedra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "canon": {"taps": MABEDRA_TAPS},
+            "torch_dtype": "bfloat16", "layers": layers}
+
+
+def run_mabedra(args) -> dict:
+    """Prefill and decode of Mabedra at layer sizes of real models (random weights), beside Qwen3 (the closest design: every
+    layer is softmax attention over paged keys and values with normed, rotated heads) and Ropulix (windows and routed
+    experts) at equal width, active feed-forward size, attention columns and depth, through the same engine; then the new
+    kernels alone against the bytes or flops they must move, each beside the like kernel of those paths."""
+
+    peak, timed, measure = _engine_measurer(args)
+    results = {}
+    for name in (() if args.only == "kernels" else args.size.split(",") if args.size else SORULIX_SIZES):
+        shape = SORULIX_SIZES[name]
+        results[name] = {"shape": dict(zip(("width", "ff", "heads", "kv_heads", "head_dim", "layer_pairs", "vocab"), shape)),
+                         "experts": MABEDRA_EXPERTS, "top": MABEDRA_TOP, "window": MABEDRA_WINDOW, "taps": MABEDRA_TAPS,
+                         "mabedra": measure(_mabedra_config(*shape), shape[-1])}
+        if args.only not in ("prefill", "decode"):
+            results[name]["qwen3_equal_size"] = measure(_qwen3_like(*shape), shape[-1])
+            results[name]["ropulix_equal_size"] = measure(_ropulix_config(*shape), shape[-1])
+    kernels = _mabedra_kernels(peak, timed) if args.only in ("all", "kernels") else {}
+    return {"workload": "mabedra", "context": CONTEXT, "steps": args.steps, "warmup": max(args.warmup, 3), "dtype": "bfloat16",
+            "data": "synthetic token ids, seeded random weights", "peaks": peak, "models": results, "kernels": kernels}
+
+
+def _mabedra_kernels(peak, timed) -> dict:
+    """Each new kernel alone at the 4k shape (width 4096; 16 heads of two maps of 128 with values of 256, 4 key/value heads),
+    replayed from a CUDA graph, beside the kernel of an existing path that does the like work (32 heads of 128, 8 key/value
+    heads: projections and cache rows of equal size)."""
+
+    import torch
+    from types import SimpleNamespace
+
+    from llm_runtime_study_b200.ops import attention_bf16, attention_diff
+    from llm_runtime_study_b200.ops import block_steps as B
+    from llm_runtime_study_b200.ops import functional as F
+    from llm_runtime_study_b200.ops import sequence_state as S
+
+    dev = "cuda:0"
+    width, heads, kv_heads, d, page, window = 4096, 32, 8, 128, PAGE_SIZE, MABEDRA_WINDOW
+    dh, dkv, dv = heads // 2, kv_heads // 2, 2 * d
+    out = {}
+    cold = timed
+
+    def timed(fn, repeat):
+        fn()
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        graph.replay()
+        return cold(graph.replay, repeat)
+
+    bf = lambda *shape: torch.randn(*shape, device=dev).bfloat16()
+
+    def case(lengths, q_lens):
+        seqs = len(lengths)
+        per = -(-max(lengths) // page)
+        table = torch.arange(seqs * per, dtype=torch.int32).view(seqs, per).to(dev)
+        positions = torch.cat([torch.arange(m - k, m) for m, k in zip(lengths, q_lens)]).int().to(dev)
+        entry = torch.cat([torch.full((k,), i) for i, k in enumerate(q_lens)]).int().to(dev)
+        ctx = SimpleNamespace(positions=positions, token_entry=entry, all_decode=max(q_lens) == 1, num_entries=seqs, q_lens=list(q_lens),
+                              kv_lens=list(lengths), max_kv_len=max(lengths), max_q_len=max(q_lens),
+                              kv_len=torch.tensor(lengths, dtype=torch.int32, device=dev), live_parts=None)
+        pools = dict(diff_k=bf(seqs * per, dkv, page, 2 * d), diff_v=bf(seqs * per, dkv, page, dv),
+                     keys=bf(seqs * per, kv_heads, page, d), values=bf(seqs * per, kv_heads, page, d))
+        return ctx, table, pools, positions
+
+    def run_diff(q, pools, ctx, table):
+        return attention_diff.diff_attention_mma(q, pools["diff_k"], pools["diff_v"], ctx, table, scale=d ** -0.5, window=window, lam=0.4,
+                                                 out_scale=0.7, eps=1e-6)
+
+    for tokens in (2048, 8192):
+        ctx, table, pools, positions = case([tokens], [tokens])
+        seen = sum(min(window, p + 1) for p in positions.tolist())
+        q, q_plain = bf(tokens, dh, 2 * d), bf(tokens, heads, d)
+        t = timed(lambda: run_diff(q, pools, ctx, table), 5)
+        plain_tiles = attention_bf16.tile_map(ctx.q_lens, 64 // min(heads // kv_heads, 16), dev, ctx.kv_lens)
+        t_plain = timed(lambda: attention_bf16.prefill_attention(q_plain, pools["keys"], pools["values"], positions=ctx.positions, block_table=table,
+                                                                 q_lens=ctx.q_lens, scale=d ** -0.5, window=window, tiles=plain_tiles), 5)
+        flops, flops_plain = 2.0 * dh * seen * 2 * (d + dv), 2.0 * heads * seen * 2 * d
+        out[f"differential_attention_prefill_{tokens}_window_{window}"] = {
+            "ms": round(t, 3), "plain_windowed_mma_ms": round(t_plain, 3), "tflops": round(flops / t / 1e9, 1),
+            "plain_windowed_mma_tflops": round(flops_plain / t_plain / 1e9, 1),
+            "of_measured_bf16_burst": {"differential": round(flops / t / 1e9 / peak["bf16_tflops"], 4),
+                                       "plain_windowed_mma": round(flops_plain / t_plain / 1e9 / peak["bf16_tflops"], 4)}}
+    for batch, length in ((8, 2048), (32, 8192)):
+        ctx, table, pools, _ = case([length] * batch, [1] * batch)
+        q, q_plain = bf(batch, dh, 2 * d), bf(batch, heads, d)
+        t = timed(lambda: run_diff(q, pools, ctx, table), 20)
+        cache = SimpleNamespace(keys=pools["keys"], values=pools["values"])
+        t_plain = timed(lambda: attention_bf16.try_paged_attention(q_plain, cache, ctx, table, scale=d ** -0.5, window=window), 20)
+        moved = 2.0 * batch * min(length, window) * (dkv * (2 * d + dv))        # equal to the plain cache's rows
+        out[f"differential_attention_decode_b{batch}_ctx{length}_window_{window}"] = {
+            "us": round(t * 1e3, 1), "plain_windowed_us": round(t_plain * 1e3, 1), "rows_read_mb": round(moved / 1e6, 2),
+            "of_measured_copy": {"differential": round(moved / t / 1e6 / peak["hbm_gbs"], 3),
+                                 "plain_windowed": round(moved / t_plain / 1e6 / peak["hbm_gbs"], 3)}}
+    # the head of a layer: the norm, both sublayers' inputs with their convolutions, the kept inputs; beside add-and-normalise
+    rows, taps = 2048, MABEDRA_TAPS
+    resid, delta, w = torch.randn(rows, width, device=dev), torch.randn(rows, width, device=dev), torch.randn(width, device=dev)
+    wa, wb = torch.randn(width, taps, device=dev), torch.randn(width, taps, device=dev)
+    kept = torch.zeros(2, taps - 1, width, device=dev)
+    q_start = torch.tensor([0, rows], dtype=torch.int32, device=dev)
+    slots, entry = torch.zeros(1, dtype=torch.int32, device=dev), torch.zeros(rows, dtype=torch.int32, device=dev)
+
+    def head_of_layer():
+        h = B.layer_norm(resid, delta, w, 1e-6, torch.float32)
+        pair = B.taps_pair(h, wa, wb, kept, q_start=q_start, slots=slots, token_entry=entry, out_dtype=torch.bfloat16)
+        S.conv_state_update(h, kept, q_start, slots)
+        return pair
+
+    t_norm = timed(lambda: B.layer_norm(resid, delta, w, 1e-6, torch.float32), 20)
+    t_head = timed(head_of_layer, 20)
+    t_old = timed(lambda: F.add_rmsnorm(resid, delta, w, 1e-6, torch.bfloat16), 20)
+    cell = rows * width
+    out["layer_head_2048x4096"] = {
+        "layer_norm_us": round(t_norm * 1e3, 1), "norm_taps_kept_us": round(t_head * 1e3, 1), "add_rmsnorm_us": round(t_old * 1e3, 1),
+        "of_measured_copy": {"layer_norm": round(cell * 16 / t_norm / 1e6 / peak["hbm_gbs"], 3),
+                             "norm_taps_kept": round(cell * (16 + 4 + 4) / t_head / 1e6 / peak["hbm_gbs"], 3),
+                             "add_rmsnorm": round(cell * 14 / t_old / 1e6 / peak["hbm_gbs"], 3)}}
+    # the tail of a layer: both sublayers' results scaled and added, the result kept, the average over all results so far
+    a, b, sa, sb = torch.randn(rows, width, device=dev), torch.randn(rows, width, device=dev), torch.randn(width, device=dev), torch.randn(width, device=dev)
+    for index in (0, 3):
+        results, mix = torch.randn(index + 2, rows, width, device=dev), torch.randn(index + 2, device=dev)
+        t = timed(lambda: B.scale_sum_average(resid, a, sa, b, sb, results, mix, index), 20)
+        moved = cell * 4 * (3 + 1 + (index + 1) + 1)       # x, a, b read; the result written; earlier results read; x written
+        out[f"layer_tail_2048x4096_over_{index + 2}"] = {"us": round(t * 1e3, 1), "of_measured_copy": round(moved / t / 1e6 / peak["hbm_gbs"], 3)}
+    # the activations: normalised powers over a row of the dense feed-forward; the gated unit with a factor per row
+    ff = 12288 * 3 // 2
+    z = bf(rows, ff)
+    coef = torch.tensor([0.9, -0.4, 0.3, 0.1], device=dev)
+    gate_up = bf(rows, 2 * 12288)
+    factor = torch.rand(rows, device=dev)
+    t_poly = timed(lambda: B.poly_norm(z, coef, 1e-6), 20)
+    t_scaled = timed(lambda: B.silu_mul_scaled(gate_up, None, factor), 20)
+    t_silu = timed(lambda: F.silu_mul(gate_up), 20)
+    out["activations_2048_rows"] = {
+        "poly_norm_us": round(t_poly * 1e3, 1), "silu_mul_scaled_us": round(t_scaled * 1e3, 1), "silu_mul_us": round(t_silu * 1e3, 1),
+        "of_measured_copy": {"poly_norm": round(rows * ff * 4 / t_poly / 1e6 / peak["hbm_gbs"], 3),
+                             "silu_mul_scaled": round(rows * 12288 * 6 / t_scaled / 1e6 / peak["hbm_gbs"], 3),
+                             "silu_mul": round(rows * 12288 * 6 / t_silu / 1e6 / peak["hbm_gbs"], 3)}}
+    # norm, rotation and page write of both maps beside the plain heads' (rows of equal width)
+    ctx, table, pools, positions = case([rows], [rows])
+    qkv, qkv_plain = bf(rows, (dh + dkv) * 2 * d + dkv * dv), bf(rows, (heads + 2 * kv_heads) * d)
+    hw = torch.ones(d, device=dev)
+    inv_freq = (10000.0 ** (-torch.arange(0, d, 2, dtype=torch.float32) / d)).to(dev)
+    t_maps = timed(lambda: attention_diff.map_norm_rope_write(
+        qkv, num_q_heads=dh, num_kv_heads=dkv, maps=2, head_dim=d, value_dim=dv, q_weight=hw, k_weight=hw, eps=1e-6, inv_freq=inv_freq,
+        rotary_dim=d, positions=positions, token_entry=ctx.token_entry, block_table=table, page_size=page, k_pool=pools["diff_k"],
+        v_pool=pools["diff_v"]), 20)
+    t_heads = timed(lambda: F.qk_norm_rope_write(
+        qkv_plain, num_q_heads=heads, num_kv_heads=kv_heads, head_dim=d, q_weight=hw, k_weight=hw, eps=1e-6, inv_freq=inv_freq, rotary_dim=d,
+        positions=positions, token_entry=ctx.token_entry, block_table=table, page_size=page, k_pool=pools["keys"], v_pool=pools["values"]), 20)
+    moved = rows * (heads + 2 * kv_heads) * d * 4
+    out["norm_rotate_write_2048_tokens"] = {"maps_us": round(t_maps * 1e3, 1), "plain_heads_us": round(t_heads * 1e3, 1),
+                                            "of_measured_copy": {"maps": round(moved / t_maps / 1e6 / peak["hbm_gbs"], 3),
+                                                                 "plain_heads": round(moved / t_heads / 1e6 / peak["hbm_gbs"], 3)}}
+    return out
+
+
 def run_reference(args) -> dict:
     """The unmodified reference from baseline/_ref: its own Qwen3ForCausalLM, paged cache,
     CUDA-graph decode and BatchScheduler, driven through Engine.create_scheduler()."""
@@ -1018,11 +1194,12 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--context", type=int, default=0, help="with --only decode: cached tokens per request (default 2048)")
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (named in config)")
-    parser.add_argument("--workload", choices=("default", "staggered14b", "decode32b", "sorulix", "ropulix"), default="default",
+    parser.add_argument("--workload", choices=("default", "staggered14b", "decode32b", "sorulix", "ropulix", "mabedra"), default="default",
                         help="default: Qwen3-8B decode/prefill; staggered14b, decode32b: the larger configurations (either --impl); "
                              "sorulix: the Sorulix design beside Qwen3 at equal sizes, and its kernels alone; "
-                             "ropulix: the Ropulix design beside Sorulix and Qwen3 at equal sizes, and its kernels alone")
-    parser.add_argument("--size", default="", help="with --workload sorulix or ropulix: sizes to run, with commas (2k, 4k; default both)")
+                             "ropulix: the Ropulix design beside Sorulix and Qwen3 at equal sizes, and its kernels alone; "
+                             "mabedra: the Mabedra design beside Qwen3 and Ropulix at equal sizes, and its kernels alone")
+    parser.add_argument("--size", default="", help="with --workload sorulix, ropulix or mabedra: sizes to run, with commas (2k, 4k; default both)")
     parser.add_argument("--only", choices=("all", "decode", "prefill", "kernels", "models"), default="all",
                         help="run only the decode steps or only the prefill (for profiler captures of a small case); "
                              "with --workload sorulix: only the kernels alone, or only the whole models")
@@ -1044,6 +1221,11 @@ def main() -> int:
             result = _unavailable("the reference has no model of this design")
         else:
             result = run_ropulix(args)
+    elif args.workload == "mabedra":
+        if args.impl == "reference":
+            result = _unavailable("the reference has no model of this design")
+        else:
+            result = run_mabedra(args)
     else:
         result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result))
