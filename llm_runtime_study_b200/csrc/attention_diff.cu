@@ -12,18 +12,45 @@
 
 namespace b200 {
 
-constexpr int kPrepWarps = 4;
+constexpr int kPrepWarps = 8;
+
+// W neighbouring values in one access (W = 1 or 4; with 4 the address is a multiple of four values).
+template <int W, typename T> __device__ __forceinline__ void load_values(const T* p, float* f);
+template <> __device__ __forceinline__ void load_values<1, float>(const float* p, float* f) { f[0] = *p; }
+template <> __device__ __forceinline__ void load_values<1, __nv_bfloat16>(const __nv_bfloat16* p, float* f) { f[0] = __bfloat162float(*p); }
+template <> __device__ __forceinline__ void load_values<4, float>(const float* p, float* f) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+}
+template <> __device__ __forceinline__ void load_values<4, __nv_bfloat16>(const __nv_bfloat16* p, float* f) {
+  const uint2 v = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+template <int W, typename T> __device__ __forceinline__ void store_values(T* p, const float* f);
+template <> __device__ __forceinline__ void store_values<1, float>(float* p, const float* f) { *p = f[0]; }
+template <> __device__ __forceinline__ void store_values<1, __nv_bfloat16>(__nv_bfloat16* p, const float* f) { *p = __float2bfloat16_rn(f[0]); }
+template <> __device__ __forceinline__ void store_values<4, float>(float* p, const float* f) {
+  *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+}
+template <> __device__ __forceinline__ void store_values<4, __nv_bfloat16>(__nv_bfloat16* p, const float* f) {
+  uint2 v;
+  *reinterpret_cast<__nv_bfloat162*>(&v.x) = __floats2bfloat162_rn(f[0], f[1]);
+  *reinterpret_cast<__nv_bfloat162*>(&v.y) = __floats2bfloat162_rn(f[2], f[3]);
+  *reinterpret_cast<uint2*>(p) = v;
+}
 
 // Row layout [q: nq * maps * d | k: nkv * maps * d | v: nkv * dv].  One warp per (token, head map) of q and k, and per
-// value head for the copy of v.
-template <typename T>
+// value head for the copy of v; a lane moves W neighbouring values at a time.
+template <typename T, int W>
 __global__ void __launch_bounds__(kPrepWarps * 32)
 map_norm_rope_write_kernel(const T* __restrict__ rows, int ld, T* __restrict__ q_out, const float* __restrict__ q_w,
                            const float* __restrict__ k_w, float eps, const float* __restrict__ inv_freq, int rot_dims,
                            const int* __restrict__ positions, const int* __restrict__ token_entry,
                            const int* __restrict__ block_table, int table_stride, int page_size, T* __restrict__ k_pool,
                            T* __restrict__ v_pool, int nq, int nkv, int maps, int d, int dv) {
-  extern __shared__ float smem[];      // [rot_dims / 2] cos, [rot_dims / 2] sin, then d floats per warp
+  extern __shared__ __align__(16) float smem[];      // [rot_dims / 2] cos, [rot_dims / 2] sin, then d floats per warp
   pdl_trigger();
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -45,7 +72,11 @@ map_norm_rope_write_kernel(const T* __restrict__ rows, int ld, T* __restrict__ q
       const int g = u - qm - km;
       const T* src = row + static_cast<size_t>(qm + km) * d + static_cast<size_t>(g) * dv;
       T* dst = v_pool + ((static_cast<size_t>(page) * nkv + g) * page_size + slot) * dv;
-      for (int i = lane; i < dv; i += 32) dst[i] = src[i];
+      for (int i = lane * W; i < dv; i += 32 * W) {
+        float f[W];
+        load_values<W>(src + i, f);
+        store_values<W>(dst + i, f);
+      }
       continue;
     }
     const bool is_q = u < qm;
@@ -53,10 +84,13 @@ map_norm_rope_write_kernel(const T* __restrict__ rows, int ld, T* __restrict__ q
     const T* src = row + static_cast<size_t>(u) * d;
     const float* w = is_q ? q_w : k_w;
     float ss = 0.f;
-    for (int i = lane; i < d; i += 32) {
-      const float v = to_float(src[i]);
-      mine[i] = v;
-      ss = fmaf(v, v, ss);
+    for (int i = lane * W; i < d; i += 32 * W) {
+      float f[W];
+      load_values<W>(src + i, f);
+#pragma unroll
+      for (int e = 0; e < W; ++e) ss = fmaf(f[e], f[e], ss);
+      if constexpr (W == 4) *reinterpret_cast<float4*>(mine + i) = make_float4(f[0], f[1], f[2], f[3]);
+      else mine[i] = f[0];
     }
     const float r = w ? rsqrtf(warp_sum(ss) / static_cast<float>(d) + eps) : 1.f;
     __syncwarp();
@@ -67,17 +101,47 @@ map_norm_rope_write_kernel(const T* __restrict__ rows, int ld, T* __restrict__ q
       const int kh = (u - qm) / maps, m = (u - qm) % maps;
       dst = k_pool + ((static_cast<size_t>(page) * nkv + kh) * page_size + slot) * (static_cast<size_t>(maps) * d) + static_cast<size_t>(m) * d;
     }
-    for (int i = lane; i < d; i += 32) {
-      const float v = mine[i] * (w ? r * w[i] : 1.f);
-      float o = v;
-      if (i < half) {
-        const float other = mine[i + half] * (w ? r * w[i + half] : 1.f);
-        o = v * cs[i] - other * sn[i];
-      } else if (i < 2 * half) {
-        const float other = mine[i - half] * (w ? r * w[i - half] : 1.f);
-        o = v * cs[i - half] + other * sn[i - half];
+    for (int i0 = lane * W; i0 < d; i0 += 32 * W) {
+      float f[W];
+      if constexpr (W == 4) {
+        // half is a multiple of four here: a chunk lies wholly in the first half, the second half or the tail
+        auto four = [](const float* q, float* o) {
+          const float4 v = *reinterpret_cast<const float4*>(q);
+          o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+        };
+        float v[4], g[4] = {1.f, 1.f, 1.f, 1.f};
+        four(mine + i0, v);
+        if (w) four(w + i0, g);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) f[e] = v[e] * (w ? r * g[e] : 1.f);
+        if (i0 < 2 * half) {
+          const bool first = i0 < half;
+          const int other = first ? i0 + half : i0 - half, a = first ? i0 : i0 - half;
+          float ov[4], og[4] = {1.f, 1.f, 1.f, 1.f}, c[4], sgn[4];
+          four(mine + other, ov);
+          if (w) four(w + other, og);
+          four(cs + a, c);
+          four(sn + a, sgn);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float o = ov[e] * (w ? r * og[e] : 1.f);
+            f[e] = first ? f[e] * c[e] - o * sgn[e] : f[e] * c[e] + o * sgn[e];
+          }
+        }
+      } else {
+        const int i = i0;
+        const float v = mine[i] * (w ? r * w[i] : 1.f);
+        float o = v;
+        if (i < half) {
+          const float other = mine[i + half] * (w ? r * w[i + half] : 1.f);
+          o = v * cs[i] - other * sn[i];
+        } else if (i < 2 * half) {
+          const float other = mine[i - half] * (w ? r * w[i - half] : 1.f);
+          o = v * cs[i - half] + other * sn[i - half];
+        }
+        f[0] = o;
       }
-      dst[i] = from_float<T>(o);
+      store_values<W>(dst + i0, f);
     }
     __syncwarp();
   }
@@ -207,10 +271,14 @@ extern "C" int b200_map_norm_rope_write(const void* rows, int ld, void* q_out, c
   if (smem > 48 * 1024) return B200_ERR_TOO_LARGE;
   const int units = (nq + nkv) * maps + nkv;
   const int blocks_y = n >= 256 ? 1 : min((units + kPrepWarps - 1) / kPrepWarps, 16);
-  B200_DISPATCH_DTYPE(dtype, T, launch(map_norm_rope_write_kernel<T>, dim3(n, blocks_y), dim3(kPrepWarps * 32), smem, stream,
-                                       static_cast<const T*>(rows), ld, static_cast<T*>(q_out), q_w, k_w, eps, inv_freq, rot_dims,
-                                       positions, token_entry, block_table, table_stride, page_size, static_cast<T*>(k_pool),
-                                       static_cast<T*>(v_pool), nq, nkv, maps, d, dv));
+  // four values an access where every head of every array starts on a multiple of four values and of 16 bytes
+  const bool wide = d % 4 == 0 && dv % 4 == 0 && ld % 4 == 0 && half % 4 == 0 &&
+                    ((reinterpret_cast<uintptr_t>(rows) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_pool) |
+                      reinterpret_cast<uintptr_t>(v_pool) | reinterpret_cast<uintptr_t>(q_w) | reinterpret_cast<uintptr_t>(k_w)) & 15) == 0;
+  B200_DISPATCH_DTYPE(dtype, T, launch(wide ? map_norm_rope_write_kernel<T, 4> : map_norm_rope_write_kernel<T, 1>, dim3(n, blocks_y),
+                                       dim3(kPrepWarps * 32), smem, stream, static_cast<const T*>(rows), ld, static_cast<T*>(q_out), q_w,
+                                       k_w, eps, inv_freq, rot_dims, positions, token_entry, block_table, table_stride, page_size,
+                                       static_cast<T*>(k_pool), static_cast<T*>(v_pool), nq, nkv, maps, d, dv));
   return launch_status();
 }
 

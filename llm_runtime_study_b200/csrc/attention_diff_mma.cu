@@ -6,12 +6,14 @@
 //
 // A CTA takes up to BM = 64 rows: consecutive query tokens of one request times the query heads that share one key/value
 // head (at most 64 of them a CTA).  Keys and values are streamed in tiles of 32 tokens through shared memory (cp.async,
-// two stages) from the request's pages.  Eight warps: warp w owns rows 16 (w & 3) .. + 15 of map (w >> 2): it forms
+// two stages, three for single tokens) from the request's pages.  Eight warps: warp w owns rows 16 (w & 3) .. + 15 of map (w >> 2): it forms
 // S = Q_m K_m^T (mma.sync m16n8k16, float accumulation), runs the online softmax in float32, rounds P to bfloat16 and
 // multiplies it with all value columns.  At the end the warps of map 2 hand their normalised rows to the warps of map 1
 // through shared memory, which subtract, normalise and store.  Single tokens may have their keys cut into parts: every
 // part leaves (maximum, sum, unnormalised output) per row and map in scratch memory and a second launch merges the parts
-// of both maps and finishes the row.
+// of both maps and finishes the row.  A single token whose heads fit 16 rows runs the second form of the kernel: the
+// four warps of a map all form the same S for rows 0 .. 15 and each multiplies P with its own quarter of the value
+// columns, so that every warp works and a thread holds a quarter of the accumulators (two CTAs a multiprocessor).
 // Key t is visible to a query at position p iff t <= p and (window == 0 or t > p - window).
 #include "common.cuh"
 #include "mma.cuh"
@@ -34,6 +36,11 @@ constexpr int OTILES = DV / 8;
 constexpr int kStreamBytes = ((BM + 2 * BN) * LDK + 2 * BN * LDV) * 2;
 constexpr int kExchangeBytes = BM * DV * 4;  // the rows of map 2, float32, after the last tile
 constexpr int kSmemBytes = kStreamBytes > kExchangeBytes ? kStreamBytes : kExchangeBytes;
+// the value columns of a single token's rows are shared out over a map's warps, an even number of 8-column tiles each
+constexpr int kColParts = OTILES % 8 == 0 ? 4 : OTILES % 4 == 0 ? 2 : 1;
+constexpr int kSingleRows = 16;
+constexpr int kSingleStages = 3;                          // its tiles are short of work, so more of them are in flight
+constexpr int kSingleSmemBytes = ((kSingleRows + kSingleStages * BN) * LDK + kSingleStages * BN * LDV) * 2;
 
 struct DiffParams {
   const bf16* q;            // [n, nq, 2 D]
@@ -51,6 +58,7 @@ struct DiffParams {
   // a tile's keys cut into `splits` parts (single tokens only): CTA z takes its share of the key tiles and leaves
   // (maximum, sum) and the unnormalised output of row (token * nq + head) * 2 + map in scratch memory
   int splits;
+  int merge;        // parts are left in scratch memory (also with one part) and a second launch finishes the rows
   float* part_o;    // [rows][splits][DV]
   float* part_ml;   // [rows][splits][2]
 };
@@ -76,12 +84,17 @@ __device__ __forceinline__ void load_tiles(bf16* ks, bf16* vs, const DiffParams&
   }
 }
 
-__global__ void __launch_bounds__(NT, 1)
+// kSingle: every tile is one token whose heads of a key/value head fit kSingleRows rows; parts go to scratch memory.
+template <bool kSingle>
+__global__ void __launch_bounds__(NT, kSingle ? 2 : 1)
 diff_attention_mma_kernel(const DiffParams p) {
+  constexpr int QROWS = kSingle ? kSingleRows : BM;
+  constexpr int STAGES = kSingle ? kSingleStages : 2;
+  constexpr int OT = kSingle ? OTILES / kColParts : OTILES;       // the output tiles of 8 columns a warp owns
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);
-  bf16* ks = qs + BM * LDK;
-  bf16* vs = ks + 2 * BN * LDK;
+  bf16* ks = qs + QROWS * LDK;
+  bf16* vs = ks + STAGES * BN * LDK;
   pdl_trigger();
   pdl_wait();
   const int tile = blockIdx.x;
@@ -91,7 +104,9 @@ diff_attention_mma_kernel(const DiffParams p) {
   const int head0 = kvh * p.group + slice * p.group_heads;
   const int* table = p.block_table + static_cast<size_t>(entry) * p.table_stride;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int rg = warp & 3, map = warp >> 2;
+  const int map = warp >> 2;
+  const int rg = kSingle ? 0 : (warp & 3);                        // the warp's 16 rows
+  const int col0 = kSingle ? (warp & 3) * OT * 8 : 0;             // its first value column
 
   // the rows of this thread: r0 = 16 rg + lane / 4 and r0 + 8; row r is token r / hg, head r % hg of the tile
   int pos[2], row_token[2], row_head[2];
@@ -110,7 +125,7 @@ diff_attention_mma_kernel(const DiffParams p) {
   // Q tile: both maps of every row
   {
     constexpr int CH = DK / 8;
-    for (int c = threadIdx.x; c < BM * CH; c += NT) {
+    for (int c = threadIdx.x; c < QROWS * CH; c += NT) {
       const int r = c / CH, ch = c - r * CH;
       const int tl = r / hg, hl = r - tl * hg;
       const bool valid = tl < count && tl < p.tokens_per_tile;
@@ -126,25 +141,31 @@ diff_attention_mma_kernel(const DiffParams p) {
     tiles = min(tiles - first_tile, per);
     t_begin += first_tile * BN;
   }
-  if (tiles > 0) load_tiles(ks, vs, p, table, kvh, t_begin, lo, hi);
-  cp_async_commit();
-
-  float o[OTILES][4];
 #pragma unroll
-  for (int j = 0; j < OTILES; ++j)
+  for (int st = 0; st < STAGES - 1; ++st) {        // one group a stage, empty ones too: the waits count groups
+    if (st < tiles) load_tiles(ks + st * BN * LDK, vs + st * BN * LDV, p, table, kvh, t_begin + st * BN, lo, hi);
+    cp_async_commit();
+  }
+
+  float o[OT][4];
+#pragma unroll
+  for (int j = 0; j < OT; ++j)
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   // a warp none of whose rows is a (token, head) of the tile only helps with the copies
-  const bool warp_live = (rg * 16) / hg < min(count, p.tokens_per_tile);
+  const bool warp_live = kSingle ? (warp & 3) < kColParts : (rg * 16) / hg < min(count, p.tokens_per_tile);
 
   for (int kt = 0; kt < tiles; ++kt) {
     const int t0 = t_begin + kt * BN;
-    const bf16* kcur = ks + (kt & 1) * BN * LDK;
-    const bf16* vcur = vs + (kt & 1) * BN * LDV;
-    if (kt + 1 < tiles) load_tiles(ks + ((kt + 1) & 1) * BN * LDK, vs + ((kt + 1) & 1) * BN * LDV, p, table, kvh, t0 + BN, lo, hi);
+    const bf16* kcur = ks + (kt % STAGES) * BN * LDK;
+    const bf16* vcur = vs + (kt % STAGES) * BN * LDV;
+    if (kt + STAGES - 1 < tiles) {
+      const int st = (kt + STAGES - 1) % STAGES;
+      load_tiles(ks + st * BN * LDK, vs + st * BN * LDV, p, table, kvh, t0 + (STAGES - 1) * BN, lo, hi);
+    }
     cp_async_commit();
-    cp_async_wait<1>();
+    cp_async_wait<STAGES - 1>();
     __syncthreads();
     if (!warp_live) {
       __syncthreads();
@@ -205,7 +226,7 @@ diff_attention_mma_kernel(const DiffParams p) {
       l[i] = l[i] * corr[i] + sum[i];
     }
 #pragma unroll
-    for (int j = 0; j < OTILES; ++j) {
+    for (int j = 0; j < OT; ++j) {
       o[j][0] *= corr[0]; o[j][1] *= corr[0];
       o[j][2] *= corr[1]; o[j][3] *= corr[1];
     }
@@ -218,9 +239,9 @@ diff_attention_mma_kernel(const DiffParams p) {
       a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
       a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
-      for (int j = 0; j < OTILES; j += 2) {
+      for (int j = 0; j < OT; j += 2) {
         uint32_t b[4];
-        ldmatrix_x4_trans(b, vcur + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDV + j * 8 + (lane >> 4) * 8);
+        ldmatrix_x4_trans(b, vcur + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDV + col0 + j * 8 + (lane >> 4) * 8);
         mma_bf16(o[j], a, b[0], b[1]);
         mma_bf16(o[j + 1], a, b[2], b[3]);
       }
@@ -228,21 +249,23 @@ diff_attention_mma_kernel(const DiffParams p) {
     __syncthreads();
   }
   cp_async_wait<0>();
-  if (p.splits > 1) {
+  if (kSingle || p.merge) {
+    if (!warp_live) return;
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       if (row_token[i] < 0) continue;
       const size_t slot = ((static_cast<size_t>(row_token[i]) * p.nq + row_head[i]) * 2 + map) * p.splits + blockIdx.z;
-      if ((lane & 3) == 0) {
+      if ((lane & 3) == 0 && col0 == 0) {
         p.part_ml[slot * 2] = m[i];
         p.part_ml[slot * 2 + 1] = l[i];
       }
-      float* dst = p.part_o + slot * DV + (lane & 3) * 2;
+      float* dst = p.part_o + slot * DV + col0 + (lane & 3) * 2;
 #pragma unroll
-      for (int j = 0; j < OTILES; ++j) *reinterpret_cast<float2*>(dst + j * 8) = make_float2(o[j][i * 2], o[j][i * 2 + 1]);
+      for (int j = 0; j < OT; ++j) *reinterpret_cast<float2*>(dst + j * 8) = make_float2(o[j][i * 2], o[j][i * 2 + 1]);
     }
     return;
   }
+  if constexpr (!kSingle) {
   // map 2's rows through shared memory (the tiles are done with: every warp passed the loop's last barrier)
   float* xs = reinterpret_cast<float*>(smem_raw);
   __syncthreads();
@@ -278,6 +301,7 @@ diff_attention_mma_kernel(const DiffParams p) {
 #pragma unroll
     for (int j = 0; j < OTILES; ++j)
       *reinterpret_cast<__nv_bfloat162*>(dst + j * 8) = __floats2bfloat162_rn(o[j][i * 2] * r, o[j][i * 2 + 1] * r);
+  }
   }
 }
 
@@ -334,7 +358,7 @@ diff_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ pa
   }
 }
 
-DeviceOnce diff_once;
+DeviceOnce diff_once, diff_single_once;
 
 }  // namespace b200
 
@@ -342,8 +366,8 @@ extern "C" int b200_attention_diff_dim() { return b200::D; }
 extern "C" int b200_attention_diff_vdim() { return b200::DV; }
 
 // q [n, nq, 2 D], keys [pages, nkv, page_size, 2 D], values [pages, nkv, page_size, DV], out [n, nq, DV]; tiles: (entry, first
-// row, rows) of consecutive tokens of one entry, at most max(1, 64 / min(64, nq / nkv)) each.  splits > 1 (every tile is token t
-// alone, tile t): the keys of a token are cut into that many parts, merged by a second launch; scratch holds
+// row, rows) of consecutive tokens of one entry, at most max(1, 64 / min(64, nq / nkv)) each.  With scratch memory (every tile is
+// token t alone, tile t): the keys of a token are cut into `splits` parts (one or more), merged by a second launch; scratch holds
 // 2 * splits * (DV + 2) floats per (token, head).
 extern "C" int b200_attention_diff_bf16(const void* q, const void* k_pool, const void* v_pool, void* out, const int* positions,
                                         const int* block_table, int table_stride, int page_size, int nq, int nkv, float scale, int window,
@@ -353,8 +377,11 @@ extern "C" int b200_attention_diff_bf16(const void* q, const void* k_pool, const
   using namespace b200;
   if (num_tiles <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || window < 0 || splits < 1 || splits > 64) return B200_ERR_BAD_SIZE;
-  if (splits > 1 && (scratch == nullptr || scratch_floats < static_cast<long>(num_tiles) * nq * 2 * splits * (DV + 2))) return 10004;
-  const int status = configure_once(diff_once, diff_attention_mma_kernel, kSmemBytes);
+  const bool merge = splits > 1 || scratch != nullptr;
+  if (merge && (scratch == nullptr || scratch_floats < static_cast<long>(num_tiles) * nq * 2 * splits * (DV + 2))) return 10004;
+  const bool single = merge && nq / nkv <= kSingleRows;
+  const int status = single ? configure_once(diff_single_once, diff_attention_mma_kernel<true>, kSingleSmemBytes)
+                            : configure_once(diff_once, diff_attention_mma_kernel<false>, kSmemBytes);
   if (status != 0) return status;
   DiffParams p{};
   p.q = static_cast<const bf16*>(q);
@@ -381,15 +408,19 @@ extern "C" int b200_attention_diff_bf16(const void* q, const void* k_pool, const
   p.eps = eps;
   p.normalise = normalise;
   p.splits = splits;
-  if (splits > 1) {
+  p.merge = merge ? 1 : 0;
+  if (merge) {
     p.tokens_per_tile = 1;
     p.part_o = scratch;
     p.part_ml = scratch + static_cast<size_t>(num_tiles) * nq * 2 * splits * DV;
   }
   dim3 grid(num_tiles, nkv * p.slices, splits);
   if (grid.y > 65535) return B200_ERR_TOO_LARGE;
-  launch(diff_attention_mma_kernel, grid, dim3(NT), kSmemBytes, stream, p);
-  if (splits > 1)
+  if (single)
+    launch(diff_attention_mma_kernel<true>, grid, dim3(NT), kSingleSmemBytes, stream, p);
+  else
+    launch(diff_attention_mma_kernel<false>, grid, dim3(NT), kSmemBytes, stream, p);
+  if (merge)
     launch(diff_merge_kernel, dim3(num_tiles * nq), dim3(128), 0, stream, p.part_o, p.part_ml, p.out, splits, lambda, out_scale, eps, normalise);
   return launch_status();
 }

@@ -15,6 +15,7 @@ from .native import c_float, c_int, c_void_p, call, ptr, require, stream_ptr, ta
 # "mma": the tensor-core kernel wherever it takes the sizes; "simt": the CUDA-core kernel everywhere
 BACKEND = os.environ.get("LLM_RUNTIME_STUDY_B200_ATTENTION_DIFF", "mma")
 ROWS_PER_TILE = 64
+SINGLE_ROWS = 16          # a single token with at most this many heads a key/value head runs the kernel's second form
 
 _TABLE = {
     "b200_attention_diff_dim": [],
@@ -148,22 +149,32 @@ def diff_attention_mma(
         splits = 1
     elif splits is None:
         splits = decode_splits(n * nkv * slices, min(window, ctx.max_kv_len) if window else ctx.max_kv_len)
-    if splits > 1:
+    if splits > 1 or (decode and nq // nkv <= SINGLE_ROWS):
+        # parts in scratch memory and a merging launch; single tokens with few heads take this way with one part too,
+        # since their form of the kernel (every warp on a share of the value columns) leaves parts only
         floats = n * nq * 2 * splits * (dv + 2)
         scratch = torch.empty(floats, dtype=torch.float32, device=q.device)
     native.call("b200_attention_diff_bf16", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(), ctx.positions.data_ptr(),
                 table.data_ptr(), table.shape[1], page_size, nq, nkv, float(scale), int(window), float(lam), float(out_scale), float(eps),
                 1 if normalise else 0, tiles[0].data_ptr(), tiles[1].data_ptr(), tiles[2].data_ptr(), count, splits, ptr(scratch), floats,
-                stream_ptr(), library=library_name(d, dv), launches=2 if splits > 1 else 1)
+                stream_ptr(), library=library_name(d, dv), launches=2 if scratch is not None else 1)
     return out
 
 
-def decode_splits(ctas: int, keys: int) -> int:
-    """Into how many parts a single token's keys are cut: enough CTAs for two a multiprocessor, no part shorter than four
-    tiles of 32 keys, at most 32 parts."""
+def decode_splits(ctas: int, keys: int, per_sm: int = 2) -> int:
+    """Into how many parts a single token's keys are cut, at most 32: the count for which the launch's waves over the
+    multiprocessors (``per_sm`` CTAs each) times the tiles of 32 keys a CTA walks (and three tile times to start and end a
+    CTA) is least; the fewest parts among equals."""
 
-    wanted = -(-2 * native.sm_count() // max(ctas, 1))
-    return max(1, min(wanted, keys // 128, 32))
+    tiles = max(1, -(-keys // 32))
+    places = per_sm * native.sm_count()
+    best, least = 1, None
+    for parts in range(1, min(32, tiles) + 1):
+        waves = -(-max(ctas, 1) * parts // places)
+        cost = waves * (-(-tiles // parts) + 3)
+        if least is None or cost < least:
+            best, least = parts, cost
+    return best
 
 
 def diff_attention(q: torch.Tensor, cache, ctx, table: torch.Tensor, *, scale: float, window: int, lam: float, out_scale: float,

@@ -64,11 +64,12 @@ def _fill(pool, table, page, rows):
 
 # ------------------------------------------------------------------------------------------ kernels alone
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
-def test_layer_norm_with_the_pending_sum_and_a_gather(out_dtype):
+@pytest.mark.parametrize("width", [90, 96, 1028])
+def test_layer_norm_with_the_pending_sum_and_a_gather(out_dtype, width):
     from llm_runtime_study_b200.ops import block_steps as B
 
     torch.manual_seed(1)
-    n, width, eps = 37, 90, 1e-5
+    n, eps = 37, 1e-5
     x, delta, w = 3.0 + 2.0 * torch.randn(n, width), torch.randn(n, width), 1.0 + 0.3 * torch.randn(width)
     resid = dev(x.clone())
     got = B.layer_norm(resid, dev(delta), dev(w), eps, out_dtype).cpu().double()
@@ -86,19 +87,21 @@ def test_layer_norm_with_the_pending_sum_and_a_gather(out_dtype):
 
 
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("taps,cuts", [(4, [1, 2, 1, 9, 3, 30]), (2, [5, 1, 1]), (3, [46]), (5, [1, 1, 1, 1, 1, 1, 2])])
-def test_input_convolutions_across_cuts(out_dtype, taps, cuts):
+@pytest.mark.parametrize("taps,cuts,width", [(4, [1, 2, 1, 9, 3, 30], 24), (2, [5, 1, 1], 24), (3, [46], 24), (5, [1, 1, 1, 1, 1, 1, 2], 24),
+                                             (4, [2, 1, 700, 1, 3], 8), (3, [1, 515, 2], 12), (4, [3, 1, 20], 23), (1, [4, 1], 8)])
+def test_input_convolutions_across_cuts(out_dtype, taps, cuts, width):
     """Two requests in one batch, fed in portions shorter than the convolution's reach, their kept inputs in slots that do
-    not follow the batch's order; both sublayers' inputs against the convolution over the whole sequences."""
+    not follow the batch's order; both sublayers' inputs against the convolution over the whole sequences.  Long portions
+    take the kernel that walks runs of rows, a width that is no multiple of four and more than four taps the plain one."""
 
     from llm_runtime_study_b200.ops import block_steps as B
     from llm_runtime_study_b200.ops import sequence_state as S
 
     torch.manual_seed(taps)
-    width, total = 24, sum(cuts)
+    total = sum(cuts)
     seqs = [torch.randn(total, width), torch.randn(total, width)]
     wa, wb = torch.randn(width, taps), torch.randn(width, taps)
-    kept = torch.zeros(6, taps - 1, width, dtype=torch.float32, device=DEV)
+    kept = torch.zeros(6, taps - 1, width, dtype=torch.float32, device=DEV) if taps > 1 else None
     slots = dev(torch.tensor([4, 1], dtype=torch.int32))
     got_a, got_b = [[], []], [[], []]
     at = 0
@@ -107,7 +110,8 @@ def test_input_convolutions_across_cuts(out_dtype, taps, cuts):
         q_start = dev(torch.tensor([0, n, 2 * n], dtype=torch.int32))
         entry = dev(torch.tensor([0] * n + [1] * n, dtype=torch.int32))
         a, b = B.taps_pair(dev(h), dev(wa), dev(wb), kept, q_start=q_start, slots=slots, token_entry=entry, out_dtype=out_dtype)
-        S.conv_state_update(dev(h), kept, q_start, slots)
+        if taps > 1:
+            S.conv_state_update(dev(h), kept, q_start, slots)
         for e in range(2):
             got_a[e].append(a[e * n:(e + 1) * n].cpu().double())
             got_b[e].append(b[e * n:(e + 1) * n].cpu().double())
@@ -117,15 +121,18 @@ def test_input_convolutions_across_cuts(out_dtype, taps, cuts):
         s = s.double()
         assert (torch.cat(got_a[e]) - (s + plain.causal_taps(s, wa.double()))).abs().max() <= tol * 4
         assert (torch.cat(got_b[e]) - (s + plain.causal_taps(s, wb.double()))).abs().max() <= tol * 4
+    if taps == 1:
+        return
     assert torch.equal(kept[4].cpu(), seqs[0][total - taps + 1:]) and torch.equal(kept[1].cpu(), seqs[1][total - taps + 1:])
     assert float(kept[0].abs().max()) == 0.0 and float(kept[5].abs().max()) == 0.0        # other slots are left alone
 
 
-def test_scaled_sum_and_the_average_over_all_results():
+@pytest.mark.parametrize("width", [40, 41])
+def test_scaled_sum_and_the_average_over_all_results(width):
     from llm_runtime_study_b200.ops import block_steps as B
 
     torch.manual_seed(3)
-    n, width, depth = 19, 40, 4
+    n, depth = 19, 4
     x0 = torch.randn(n, width)
     results = torch.zeros(depth + 1, n, width, device=DEV)
     results[0] = dev(x0)
@@ -148,7 +155,7 @@ def test_scaled_sum_and_the_average_over_all_results():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("n,ff", [(33, 40), (2, 257), (5, 1024)])
+@pytest.mark.parametrize("n,ff", [(33, 40), (2, 257), (5, 1024), (2, 4104), (2, 25600)])
 def test_polynomial_activation_of_normalised_powers(dtype, n, ff):
     from llm_runtime_study_b200.ops import block_steps as B
 
@@ -181,10 +188,13 @@ def _plain_maps(x, nq, nkv, d, dv, qw, kw, eps, freqs, first=0):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("nq,nkv,d,dv,rot,page", [(3, 1, 8, 12, 4, 4), (2, 2, 16, 8, 16, 16), (4, 2, 24, 40, 0, 8), (6, 3, 64, 32, 32, 16)])
-def test_map_norm_rotation_and_page_write(dtype, nq, nkv, d, dv, rot, page):
+@pytest.mark.parametrize("extra", [3, 0])
+@pytest.mark.parametrize("nq,nkv,d,dv,rot,page", [(3, 1, 8, 12, 4, 4), (2, 2, 16, 8, 16, 16), (4, 2, 24, 40, 0, 8), (6, 3, 64, 32, 32, 16),
+                                                  (2, 1, 128, 256, 64, 16), (2, 1, 48, 80, 24, 16)])
+def test_map_norm_rotation_and_page_write(dtype, nq, nkv, d, dv, rot, page, extra):
     """Each map of q and k normed with the shared weight and rotated on its leading columns by the token's position; k and v
-    land in the request's pages.  The second request starts behind 37 cached tokens, so its positions do not start at 0."""
+    land in the request's pages.  The second request starts behind 37 cached tokens, so its positions do not start at 0.
+    Rows with columns behind them that are no multiple of four values are moved value by value, the others four at a time."""
 
     from llm_runtime_study_b200.ops import attention_diff as A
 
@@ -192,7 +202,7 @@ def test_map_norm_rotation_and_page_write(dtype, nq, nkv, d, dv, rot, page):
     lengths, q_lens, eps = [21, 50], [21, 13], 1e-5
     scaling = {"factor": 4.0, "low": 1.0, "high": 3.0, "original": 32}
     freqs = plain.scaled_frequencies(rot, 300.0, scaling, torch.float64) if rot else None
-    rows = _qkv_rows(q_lens, nq, nkv, d, dv, dtype)
+    rows = _qkv_rows(q_lens, nq, nkv, d, dv, dtype, extra)
     qw, kw = 1 + 0.2 * torch.randn(d), 1 + 0.2 * torch.randn(d)
     table, pages = _pages(d, page, lengths)
     ctx = _ctx(lengths, q_lens)
@@ -266,13 +276,16 @@ def test_differential_attention_against_plain(kind, dtype, nq, nkv, d, dv, page,
         at += n
 
 
-def test_single_tokens_whose_keys_are_cut_into_parts():
+@pytest.mark.parametrize("nq,nkv,d,dv", [(4, 2, 32, 48), (8, 2, 32, 64), (6, 1, 16, 32), (16, 1, 64, 64), (40, 2, 16, 16)])
+def test_single_tokens_whose_keys_are_cut_into_parts(nq, nkv, d, dv):
     """Three requests of unequal length, one token each: the longest is cut into several parts that a second launch merges
-    per map before the maps are subtracted; a part may hold no visible key at all (the short request)."""
+    per map before the maps are subtracted; a part may hold no visible key at all (the short request).  Up to 16 heads a
+    key/value head take the kernel's form in which a map's warps share out the value columns (in four parts, two or one by
+    the value size); more heads take the form of the prompt portions."""
 
     from llm_runtime_study_b200.ops import attention_diff as A
 
-    nq, nkv, d, dv, page = 4, 2, 32, 48, 16
+    page = 16
     lengths = [1500, 3, 700]
     for window in (0, 600):
         keys = min(window, max(lengths)) if window else max(lengths)
