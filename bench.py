@@ -984,6 +984,27 @@ def _mabedra_kernels(peak, timed) -> dict:
         graph.replay()
         return cold(graph.replay, repeat)
 
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timed_cold(fn, repeat):
+        """The same with the L2 overwritten before every replay (256 MB of zeros), each replay between events of its own: a kernel
+        whose arrays would stay in the L2 from one replay to the next is then measured from memory like one whose arrays do not."""
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        total = 0.0
+        for _ in range(repeat):
+            flush.zero_()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            graph.replay()
+            end.record()
+            torch.cuda.synchronize()
+            total += start.elapsed_time(end)
+        return total / repeat
+
     bf = lambda *shape: torch.randn(*shape, device=dev).bfloat16()
 
     def case(lengths, q_lens):
@@ -1046,11 +1067,18 @@ def _mabedra_kernels(peak, timed) -> dict:
     t_head = timed(head_of_layer, 20)
     t_old = timed(lambda: F.add_rmsnorm(resid, delta, w, 1e-6, torch.bfloat16), 20)
     cell = rows * width
+    c_norm = timed_cold(lambda: B.layer_norm(resid, delta, w, 1e-6, torch.float32), 10)
+    c_head = timed_cold(head_of_layer, 10)
+    c_old = timed_cold(lambda: F.add_rmsnorm(resid, delta, w, 1e-6, torch.bfloat16), 10)
     out["layer_head_2048x4096"] = {
         "layer_norm_us": round(t_norm * 1e3, 1), "norm_taps_kept_us": round(t_head * 1e3, 1), "add_rmsnorm_us": round(t_old * 1e3, 1),
         "of_measured_copy": {"layer_norm": round(cell * 16 / t_norm / 1e6 / peak["hbm_gbs"], 3),
                              "norm_taps_kept": round(cell * (16 + 4 + 4) / t_head / 1e6 / peak["hbm_gbs"], 3),
-                             "add_rmsnorm": round(cell * 14 / t_old / 1e6 / peak["hbm_gbs"], 3)}}
+                             "add_rmsnorm": round(cell * 14 / t_old / 1e6 / peak["hbm_gbs"], 3)},
+        "l2_flushed_us": {"layer_norm": round(c_norm * 1e3, 1), "norm_taps_kept": round(c_head * 1e3, 1), "add_rmsnorm": round(c_old * 1e3, 1)},
+        "l2_flushed_of_measured_copy": {"layer_norm": round(cell * 16 / c_norm / 1e6 / peak["hbm_gbs"], 3),
+                                        "norm_taps_kept": round(cell * (16 + 4 + 4) / c_head / 1e6 / peak["hbm_gbs"], 3),
+                                        "add_rmsnorm": round(cell * 14 / c_old / 1e6 / peak["hbm_gbs"], 3)}}
     # the tail of a layer: both sublayers' results scaled and added, the result kept, the average over all results so far
     a, b, sa, sb = torch.randn(rows, width, device=dev), torch.randn(rows, width, device=dev), torch.randn(width, device=dev), torch.randn(width, device=dev)
     for index in (0, 3):

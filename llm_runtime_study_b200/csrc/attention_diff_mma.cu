@@ -63,25 +63,31 @@ struct DiffParams {
   float* part_ml;   // [rows][splits][2]
 };
 
+// Eight threads a row: the page of the row is looked up once and each thread copies every eighth 16-byte piece of the key row
+// and of the value row.
+static_assert(NT / 8 == BN, "a tile's rows are shared out eight threads each");
 __device__ __forceinline__ void load_tiles(bf16* ks, bf16* vs, const DiffParams& p, const int* table, int kvh, int t0, int lo, int hi) {
-  constexpr int CK = DK / 8, CV = DV / 8, CH = CK + CV;
-  for (int c = threadIdx.x; c < BN * CH; c += NT) {
-    const int r = c / CH, ch = c - r * CH;
-    const int t = t0 + r;
-    const bool key = ch < CK;
-    const bf16* src = key ? p.k_pool : p.v_pool;
-    int bytes = 0;
-    if (t >= lo && t <= hi) {
-      const int index = t / p.page_size;
-      const int page = table[index];
-      if (page >= 0) {
-        const size_t row = (static_cast<size_t>(page) * p.nkv + kvh) * p.page_size + (t - index * p.page_size);
-        src += key ? row * DK + ch * 8 : row * DV + (ch - CK) * 8;
-        bytes = 16;
-      }
+  constexpr int CK = DK / 8, CV = DV / 8;
+  const int r = threadIdx.x >> 3, piece = threadIdx.x & 7;
+  const int t = t0 + r;
+  const bf16* ksrc = p.k_pool;
+  const bf16* vsrc = p.v_pool;
+  int bytes = 0;
+  if (t >= lo && t <= hi) {
+    const int index = t / p.page_size;
+    const int page = table[index];
+    if (page >= 0) {
+      const size_t row = (static_cast<size_t>(page) * p.nkv + kvh) * p.page_size + (t - index * p.page_size);
+      ksrc += row * DK;
+      vsrc += row * DV;
+      bytes = 16;
     }
-    cp_async_16(key ? ks + r * LDK + ch * 8 : vs + r * LDV + (ch - CK) * 8, src, bytes);
   }
+  const int step = bytes ? 8 : 0;          // a row that is not copied (zeros are written) reads no address but the pool's first
+#pragma unroll
+  for (int ch = piece; ch < CK; ch += 8) cp_async_16(ks + r * LDK + ch * 8, ksrc + ch * step, bytes);
+#pragma unroll
+  for (int ch = piece; ch < CV; ch += 8) cp_async_16(vs + r * LDV + ch * 8, vsrc + ch * step, bytes);
 }
 
 // kSingle: every tile is one token whose heads of a key/value head fit kSingleRows rows; parts go to scratch memory.
