@@ -312,25 +312,38 @@ diff_attention_mma_kernel(const DiffParams p) {
 }
 
 // A row's parts merged per map (a_m = sum_z 2^(m_z - M) o_z / sum_z 2^(m_z - M) l_z, M the largest maximum), then
-// o = a_1 - lambda a_2, its root mean square over the value columns, the scale.
+// o = a_1 - lambda a_2, its root mean square over the value columns, the scale.  The parts' factors are formed once, in
+// shared memory, from one load a part; the sums over the parts then run over loads that do not wait for one another.
+constexpr int kMaxSplits = 64;
 __global__ void __launch_bounds__(128)
 diff_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out, int splits, float lambda,
                   float out_scale, float eps, int normalise) {
   __shared__ float warp_ss[4];
+  __shared__ float part_m[2][kMaxSplits], part_l[2][kMaxSplits], factor[2][kMaxSplits];
   pdl_trigger();
   pdl_wait();
   const size_t row = blockIdx.x;
-  float top[2], inv[2];
-#pragma unroll
-  for (int mp = 0; mp < 2; ++mp) {
-    const float* ml = part_ml + (row * 2 + mp) * splits * 2;
-    float t = -INFINITY;
-    for (int z = 0; z < splits; ++z) t = fmaxf(t, ml[z * 2]);
-    float total = 0.f;
-    for (int z = 0; z < splits; ++z) total += ml[z * 2] == -INFINITY ? 0.f : exp2f(ml[z * 2] - t) * ml[z * 2 + 1];
-    top[mp] = t;
-    inv[mp] = total > 0.f ? 1.f / total : 0.f;
+  if (threadIdx.x < 2 * splits) {
+    const int mp = threadIdx.x / splits, z = threadIdx.x - mp * splits;
+    const float2 ml = *reinterpret_cast<const float2*>(part_ml + ((row * 2 + mp) * splits + z) * 2);
+    part_m[mp][z] = ml.x;
+    part_l[mp][z] = ml.y;
   }
+  __syncthreads();
+  if (threadIdx.x < 2) {            // one thread a map, the parts in their order
+    const int mp = threadIdx.x;
+    float t = -INFINITY;
+    for (int z = 0; z < splits; ++z) t = fmaxf(t, part_m[mp][z]);
+    float total = 0.f;
+    for (int z = 0; z < splits; ++z) {
+      const float f = part_m[mp][z] == -INFINITY ? 0.f : exp2f(part_m[mp][z] - t);
+      factor[mp][z] = f;
+      total += f * part_l[mp][z];
+    }
+    const float inv = total > 0.f ? 1.f / total : 0.f;
+    for (int z = 0; z < splits; ++z) factor[mp][z] *= inv;
+  }
+  __syncthreads();
   constexpr int PER = (DV + 127) / 128;
   float vals[PER];
   float ss = 0.f;
@@ -342,12 +355,11 @@ diff_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ pa
     float a[2];
 #pragma unroll
     for (int mp = 0; mp < 2; ++mp) {
-      const float* ml = part_ml + (row * 2 + mp) * splits * 2;
-      const float* po = part_o + (row * 2 + mp) * splits * DV;
+      const float* po = part_o + (row * 2 + mp) * splits * DV + c;
       float acc = 0.f;
-      for (int z = 0; z < splits; ++z)
-        if (ml[z * 2] != -INFINITY) acc = fmaf(exp2f(ml[z * 2] - top[mp]), po[z * DV + c], acc);
-      a[mp] = acc * inv[mp];
+#pragma unroll 8
+      for (int z = 0; z < splits; ++z) acc = fmaf(factor[mp][z], po[static_cast<size_t>(z) * DV], acc);   // a part without keys left zeros
+      a[mp] = acc;
     }
     vals[u] = a[0] - lambda * a[1];
     ss = fmaf(vals[u], vals[u], ss);
@@ -382,7 +394,7 @@ extern "C" int b200_attention_diff_bf16(const void* q, const void* k_pool, const
                                         long scratch_floats, cudaStream_t stream) {
   using namespace b200;
   if (num_tiles <= 0) return 0;
-  if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || window < 0 || splits < 1 || splits > 64) return B200_ERR_BAD_SIZE;
+  if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || window < 0 || splits < 1 || splits > kMaxSplits) return B200_ERR_BAD_SIZE;
   const bool merge = splits > 1 || scratch != nullptr;
   if (merge && (scratch == nullptr || scratch_floats < static_cast<long>(num_tiles) * nq * 2 * splits * (DV + 2))) return 10004;
   const bool single = merge && nq / nkv <= kSingleRows;
