@@ -6,7 +6,8 @@
 //
 // A CTA takes up to BM = 64 rows: consecutive query tokens of one request times the query heads that share one key/value
 // head (at most 64 of them a CTA).  Keys and values are streamed in tiles of 32 tokens through shared memory (cp.async,
-// two stages, three for single tokens) from the request's pages.  Eight warps: warp w owns rows 16 (w & 3) .. + 15 of map (w >> 2): it forms
+// two stages, three for single tokens) from the request's pages.  Eight warps: warp w owns rows 16 (w & 3) .. + 15 of
+// map (w >> 2): it forms
 // S = Q_m K_m^T (mma.sync m16n8k16, float accumulation), runs the online softmax in float32, rounds P to bfloat16 and
 // multiplies it with all value columns.  At the end the warps of map 2 hand their normalised rows to the warps of map 1
 // through shared memory, which subtract, normalise and store.  Single tokens may have their keys cut into parts: every
