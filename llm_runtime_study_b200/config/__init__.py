@@ -3,6 +3,7 @@ from .mabedra import MabedraConfig
 from .qwen3 import Qwen3Config
 from .ropulix import RopulixConfig
 from .sorulix import SorulixConfig
+from .tafisun import TafisunConfig
 from .registry import (
     Architecture,
     architecture_for,
@@ -17,6 +18,7 @@ __all__ = [
     "Qwen3Config",
     "RopulixConfig",
     "SorulixConfig",
+    "TafisunConfig",
     "architecture_for",
     "load_config",
     "optional",

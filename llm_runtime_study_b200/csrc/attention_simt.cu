@@ -12,7 +12,9 @@
 // Optional rules on the scores, each a parameter: a soft cap (S <- cap * tanh(S / cap)), a
 // bias by distance (S <- S - slope_j * (p - t) with one slope per query head), and a sink
 // (a virtual key of score 0 that carries no value: the weights become exp(S) / (1 + sum exp(S))).
-// Values may have a head size `dv` of their own.
+// Values may have a head size `dv` of their own.  Two further rules: a bias by the logarithm of the distance
+// (S <- S - r1_j * ln(1 + r2_j * (p - t)) with two numbers per query head) and a mask in blocks (`chunk` > 0: position p
+// sees t only if floor(p / chunk) = floor(t / chunk), blocks counted from position 0 of the sequence).
 #include "common.cuh"
 
 namespace b200 {
@@ -25,7 +27,8 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
                             const int* __restrict__ positions, const int* __restrict__ token_entry,
                             const int* __restrict__ block_table, int table_stride, int page_size,
                             int nq, int nkv, int d, float scale, int window, int dv, float softcap,
-                            const float* __restrict__ slopes, int sink, int v_row) {
+                            const float* __restrict__ slopes, int sink, int v_row, int chunk,
+                            const float* __restrict__ log_r1, const float* __restrict__ log_r2) {
   extern __shared__ float smem[];
   pdl_trigger();
   pdl_wait();
@@ -41,11 +44,13 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
   for (int i = lane; i < d; i += 32) qs[i] = to_float(qrow[i]);
   __syncwarp();
 
-  const int w0 = window > 0 ? max(0, p - window + 1) : 0;
+  int w0 = window > 0 ? max(0, p - window + 1) : 0;
+  if (chunk > 0) w0 = max(w0, p / chunk * chunk);
   // the sink is a key of score 0 and value 0 that every row sees: it starts the running maximum and sum
   float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;
   const float slope = slopes ? slopes[head] : 0.f;
   const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+  const float r1 = log_r1 ? log_r1[head] : 0.f, r2 = log_r2 ? log_r2[head] : 0.f;
   float acc[kMaxChunks];
 #pragma unroll
   for (int c = 0; c < kMaxChunks; ++c) acc[c] = 0.f;
@@ -73,6 +78,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
       s = dot * scale;
       if (softcap > 0.f) s = softcap * tanhf(s * inv_cap);
       s -= slope * static_cast<float>(p - t);
+      if (log_r1 != nullptr) s -= r1 * log1pf(r2 * static_cast<float>(p - t));
     }
     const float m_tile = warp_max(s);
     if (m_tile == -INFINITY) continue;
@@ -115,10 +121,19 @@ extern "C" int b200_paged_attention_simt_strided(
     const void* q, const void* k_pool, const void* v_pool, void* out, const int* positions,
     const int* token_entry, const int* block_table, int table_stride, int page_size, int n,
     int nq, int nkv, int d, int dv, int v_row, float scale, int window, float softcap, const float* slopes, int sink,
-    int dtype, cudaStream_t stream) {
+    int dtype, cudaStream_t stream);
+
+// The same with the mask in blocks (chunk <= 0: none) and the bias by the logarithm of the distance (log_r1, log_r2:
+// [nq] floats each, or both null).
+extern "C" int b200_paged_attention_simt_masked(
+    const void* q, const void* k_pool, const void* v_pool, void* out, const int* positions,
+    const int* token_entry, const int* block_table, int table_stride, int page_size, int n,
+    int nq, int nkv, int d, int dv, int v_row, float scale, int window, float softcap, const float* slopes, int sink,
+    int chunk, const float* log_r1, const float* log_r2, int dtype, cudaStream_t stream) {
   using namespace b200;
   if (n <= 0) return 0;
-  if (d <= 0 || dv <= 0 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || v_row < dv)
+  if (d <= 0 || dv <= 0 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || v_row < dv ||
+      (log_r1 == nullptr) != (log_r2 == nullptr))
     return B200_ERR_BAD_SIZE;
   if (dv > 32 * 20 || d > 2048) return B200_ERR_TOO_LARGE;
   dim3 grid(n, (nq + 3) / 4);
@@ -129,13 +144,23 @@ extern "C" int b200_paged_attention_simt_strided(
       launch(paged_attention_simt_kernel<T, CH>, dim3(grid), dim3(128), smem, stream,                       \
           static_cast<const T*>(q), static_cast<const T*>(k_pool), static_cast<const T*>(v_pool),          \
           static_cast<T*>(out), positions, token_entry, block_table, table_stride, page_size, nq,           \
-          nkv, d, scale, window, dv, softcap, slopes, sink, v_row))
+          nkv, d, scale, window, dv, softcap, slopes, sink, v_row, chunk, log_r1, log_r2))
   if (dv <= 64) { B200_SIMT_ATTENTION(2); }
   else if (dv <= 128) { B200_SIMT_ATTENTION(4); }
   else if (dv <= 256) { B200_SIMT_ATTENTION(8); }
   else { B200_SIMT_ATTENTION(20); }
 #undef B200_SIMT_ATTENTION
   return launch_status();
+}
+
+extern "C" int b200_paged_attention_simt_strided(
+    const void* q, const void* k_pool, const void* v_pool, void* out, const int* positions,
+    const int* token_entry, const int* block_table, int table_stride, int page_size, int n,
+    int nq, int nkv, int d, int dv, int v_row, float scale, int window, float softcap, const float* slopes, int sink,
+    int dtype, cudaStream_t stream) {
+  return b200_paged_attention_simt_masked(q, k_pool, v_pool, out, positions, token_entry, block_table, table_stride, page_size,
+                                          n, nq, nkv, d, dv, v_row, scale, window, softcap, slopes, sink, 0, nullptr, nullptr,
+                                          dtype, stream);
 }
 
 extern "C" int b200_paged_attention_simt_rules(

@@ -792,6 +792,35 @@ __global__ void glu_limit_vec_kernel(const T* __restrict__ gate_up, T* __restric
   *reinterpret_cast<V*>(out + static_cast<size_t>(blockIdx.y) * inter + i) = Vec<T>::pack(y);
 }
 
+// out = relu(x)^2, element by element (float32 arithmetic, rounded once)
+template <typename T>
+__global__ void relu2_kernel(const T* __restrict__ x, T* __restrict__ out, size_t count) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= count) return;
+  const float v = fmaxf(to_float(x[i]), 0.f);
+  out[i] = from_float<T>(v * v);
+}
+
+template <typename T>
+__global__ void relu2_vec_kernel(const T* __restrict__ x, T* __restrict__ out, size_t vectors) {
+  constexpr int VN = Vec<T>::n;
+  using V = typename Vec<T>::type;
+  pdl_trigger();
+  pdl_wait();
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= vectors) return;
+  float f[VN];
+  Vec<T>::unpack(reinterpret_cast<const V*>(x)[i], f);
+#pragma unroll
+  for (int e = 0; e < VN; ++e) {
+    const float v = fmaxf(f[e], 0.f);
+    f[e] = v * v;
+  }
+  reinterpret_cast<V*>(out)[i] = Vec<T>::pack(f);
+}
+
 // out[t] (+)= factor * x[t] * rsqrt(mean(x[t]^2) + eps) * w.  With `cached` the row is kept in shared memory
 // between the two passes (16-byte accesses; the width is then a multiple of 4 and the rows start on 16 bytes).
 __global__ void rmsnorm_accumulate_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ out,
@@ -873,6 +902,24 @@ extern "C" int b200_glu_limit(const void* gate_up, void* out, int n, int inter, 
       launch(glu_limit_vec_kernel<T>, grid, dim3(256), 0, stream, static_cast<const T*>(gate_up), static_cast<T*>(out), inter, limit, alpha);
     } else {
       launch(glu_limit_kernel<T>, dim3(n), dim3(256), 0, stream, static_cast<const T*>(gate_up), static_cast<T*>(out), inter, limit, alpha);
+    }
+  });
+  return launch_status();
+}
+
+extern "C" int b200_relu2(const void* x, void* out, long long count, int dtype, cudaStream_t stream) {
+  using namespace b200;
+  if (count <= 0) return 0;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  B200_DISPATCH_DTYPE(dtype, T, {
+    constexpr int VN = Vec<T>::n;
+    if (aligned && count % VN == 0) {
+      const size_t vectors = static_cast<size_t>(count) / VN;
+      launch(relu2_vec_kernel<T>, dim3(static_cast<unsigned>((vectors + 255) / 256)), dim3(256), 0, stream, static_cast<const T*>(x),
+             static_cast<T*>(out), vectors);
+    } else {
+      launch(relu2_kernel<T>, dim3(static_cast<unsigned>((count + 255) / 256)), dim3(256), 0, stream, static_cast<const T*>(x),
+             static_cast<T*>(out), static_cast<size_t>(count));
     }
   });
   return launch_status();

@@ -251,12 +251,22 @@ int launch_grouped_mma(const GroupedArgs& g, int batch, int act, cudaStream_t st
 // the `top` largest (the lower index wins a tie), weights = softmax over the chosen logits only.  Every thread sums its
 // share of the row for eight experts at a time; the shares meet in a warp's shuffle tree and then warp by warp in order, so
 // a token's logits do not depend on the batch around it.
+//
+// score 2: s = softmax(z) over all outputs; the choice goes by s + correction (a float per output, may be null); the outputs
+// form `groups` equal groups of neighbours, a group scores the largest choice score in it, and only outputs of the `keep`
+// best groups can be chosen (the lower index wins a tie, as everywhere); weights = s (without the correction) * scale.
+// The router's matrix may hold `extra` further rows behind those of the outputs (one number per token each: a gate on
+// something that runs for every token); their logits' sigmoids go to extra_out [n, extra] and take no part in the choice.
 template <typename T>
 __global__ void __launch_bounds__(128)
 route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ br, int* __restrict__ ids,
-             float* __restrict__ wts, int width, int experts, int top, int score) {
-  extern __shared__ float logits[];          // [experts], then [4][8] partial sums
+             float* __restrict__ wts, int width, int outputs, int top, int score, const float* __restrict__ correction, int groups,
+             int keep, float scale, int extra, float* __restrict__ extra_out) {
+  extern __shared__ float logits[];          // [experts], then [4][8] partial sums, then [outputs] probabilities, [groups] scores
+  const int experts = outputs + extra;       // rows of the router's matrix
   float* part = logits + experts;
+  float* probs = part + 32;
+  float* group_score = probs + outputs;
   pdl_trigger();
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -297,12 +307,61 @@ route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float*
     __syncthreads();
   }
   if (warp != 0) return;
+  if (lane < extra) extra_out[static_cast<size_t>(token) * extra + lane] = 1.f / (1.f + expf(-logits[outputs + lane]));
+  if (score == 2) {
+    float mx = -INFINITY;
+    for (int e = lane; e < outputs; e += 32) mx = fmaxf(mx, logits[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < outputs; e += 32) {
+      const float p = expf(logits[e] - mx);
+      probs[e] = p;
+      sum += p;
+    }
+    sum = warp_sum(sum);
+    __syncwarp();
+    for (int e = lane; e < outputs; e += 32) {
+      const float p = probs[e] / sum;
+      probs[e] = p;
+      logits[e] = p + (correction ? correction[e] : 0.f);
+    }
+    __syncwarp();
+    if (groups > 1) {
+      const int per = outputs / groups;
+      for (int g = lane; g < groups; g += 32) {
+        float best = -INFINITY;
+        for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, logits[e]);
+        group_score[g] = best;
+      }
+      __syncwarp();
+      for (int j = 0; j < keep; ++j) {          // the kept groups are marked by +infinity
+        float best = -INFINITY;
+        int at = 0x7fffffff;
+        for (int g = lane; g < groups; g += 32) {
+          const float v = group_score[g];
+          if (v != INFINITY && v > best) { best = v; at = g; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+          const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+          if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+        }
+        __syncwarp();
+        if (lane == 0 && at < groups) group_score[at] = INFINITY;
+        __syncwarp();
+      }
+      for (int e = lane; e < outputs; e += 32)
+        if (group_score[e / per] != INFINITY) logits[e] = -INFINITY;
+      __syncwarp();
+    }
+  }
   float first = 0.f, total = 0.f, mine = 0.f, mine_logit = 0.f;
   int my_id = 0;
   for (int j = 0; j < top; ++j) {
     float best = -INFINITY;
     int at = 0x7fffffff;
-    for (int e = lane; e < experts; e += 32) {
+    for (int e = lane; e < outputs; e += 32) {
       const float v = logits[e];
       if (v > best) { best = v; at = e; }       // ascending e: the first of equals stays
     }
@@ -317,19 +376,25 @@ route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float*
     total += p;
     if (lane == j) { mine = p; mine_logit = best; my_id = at; }
     __syncwarp();
-    if (lane == 0) logits[at] = -INFINITY;
+    if (lane == 0 && at < outputs) logits[at] = -INFINITY;
     __syncwarp();
   }
   if (lane < top) {
+    my_id = min(my_id, outputs - 1);          // nothing left to choose from (every score NaN): still a valid output
     ids[static_cast<size_t>(token) * top + lane] = my_id;
-    // score 0: the softmax over the chosen logits; 1: each chosen logit's own sigmoid (the order of sigmoids is the logits')
-    wts[static_cast<size_t>(token) * top + lane] = score == 1 ? 1.f / (1.f + expf(-mine_logit)) : mine / total;
+    // score 0: the softmax over the chosen logits; 1: each chosen logit's own sigmoid (the order of sigmoids is the logits');
+    // 2: the chosen output's share of the softmax over all outputs, times scale
+    float w = mine / total;
+    if (score == 1) w = 1.f / (1.f + expf(-mine_logit));
+    if (score == 2) w = probs[my_id] * scale;
+    wts[static_cast<size_t>(token) * top + lane] = w;
   }
 }
 
 // One CTA.  Counts the pairs of every expert, lays the experts' rows out one behind the other, each padded to whole
 // tiles of BM rows, and gives every pair its row: sorted_token[row] = token (-1 in the padding), pair_row[pair] = row,
 // tile_group[tile] = expert (-1 behind the last used tile).  A tile has tile_rows rows (what the product kernel takes).
+// A pair whose id is `experts` or more (a router output without an expert behind it) gets no row: pair_row = -1.
 __global__ void __launch_bounds__(1024)
 plan_kernel(const int* __restrict__ ids, int pairs, int top, int experts, int* __restrict__ sorted_token, int* __restrict__ pair_row,
             int* __restrict__ tile_group, int max_tiles, int tile_rows) {
@@ -341,7 +406,8 @@ plan_kernel(const int* __restrict__ ids, int pairs, int top, int experts, int* _
   for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
   for (int r = threadIdx.x; r < max_tiles * tile_rows; r += blockDim.x) sorted_token[r] = -1;
   __syncthreads();
-  for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&count[ids[p]], 1);
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x)
+    if (ids[p] < experts) atomicAdd(&count[ids[p]], 1);
   __syncthreads();
   if (threadIdx.x == 0) {
     int at = 0;
@@ -368,6 +434,7 @@ plan_kernel(const int* __restrict__ ids, int pairs, int top, int experts, int* _
   }
   for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
     const int e = ids[p];
+    if (e >= experts) { pair_row[p] = -1; continue; }
     const int row = start[e] + atomicAdd(&count[e], 1);
     sorted_token[row] = p / top;
     pair_row[p] = row;
@@ -387,6 +454,31 @@ combine_kernel(const float* __restrict__ rows, const int* __restrict__ pair_row,
       const int p = token * top + j;
       acc = fmaf(wts ? wts[p] : 1.f, rows[static_cast<size_t>(pair_row[p]) * width + c], acc);
     }
+    out[static_cast<size_t>(token) * width + c] = acc;
+  }
+}
+
+// The same where a pair may have no row (pair_row < 0: the router output returns the token's own input row x[t]) and a
+// further row per token is added with a factor of its own: out[t] = sum_j wts[t, j] * (rows[pair_row[t, j]] or x[t]) +
+// extra_scale[t] * extra[t].  x in the activation type; extra float32 or null.
+template <typename T>
+__global__ void __launch_bounds__(256)
+combine_mixed_kernel(const float* __restrict__ rows, const int* __restrict__ pair_row, const float* __restrict__ wts,
+                     const T* __restrict__ x, const float* __restrict__ extra, const float* __restrict__ extra_scale,
+                     float* __restrict__ out, int width, int top) {
+  pdl_trigger();
+  pdl_wait();
+  const int token = blockIdx.x;
+  const float es = extra != nullptr ? extra_scale[token] : 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < top; ++j) {
+      const int p = token * top + j;
+      const int r = pair_row[p];
+      const float v = r >= 0 ? rows[static_cast<size_t>(r) * width + c] : to_float(x[static_cast<size_t>(token) * width + c]);
+      acc = fmaf(wts[p], v, acc);
+    }
+    if (extra != nullptr) acc = fmaf(es, extra[static_cast<size_t>(token) * width + c], acc);
     out[static_cast<size_t>(token) * width + c] = acc;
   }
 }
@@ -443,15 +535,26 @@ extern "C" int b200_gemm_grouped(const void* A, long long lda, long long a_z, co
   return B200_ERR_BAD_DTYPE;
 }
 
-extern "C" int b200_moe_route(const void* h, const float* wr, const float* br, int* ids, float* wts, int n, int width, int experts,
-                              int top, int score, int dtype, cudaStream_t stream) {
+// wr float32 [outputs + extra, width]; score 0, 1 or 2 (see route_kernel); correction [outputs] or null; extra_out [n, extra].
+extern "C" int b200_moe_route_grouped(const void* h, const float* wr, const float* br, const float* correction, int* ids, float* wts,
+                                      float* extra_out, int n, int width, int outputs, int top, int score, int groups, int keep,
+                                      float scale, int extra, int dtype, cudaStream_t stream) {
   using namespace b200;
   if (n <= 0) return 0;
-  if (width <= 0 || experts <= 0 || top <= 0 || top > experts || top > 32 || experts > 2048) return B200_ERR_BAD_SIZE;
-  const size_t smem = sizeof(float) * (experts + 32);
+  if (width <= 0 || outputs <= 0 || top <= 0 || top > outputs || top > 32 || outputs > 2048 || extra < 0 || extra > 32 ||
+      (extra > 0 && extra_out == nullptr) || groups <= 0 || outputs % groups != 0 || keep <= 0 || keep > groups ||
+      top > keep * (outputs / groups) || score < 0 || score > 2 || (groups > 1 && score != 2))
+    return B200_ERR_BAD_SIZE;
+  const size_t smem = sizeof(float) * (outputs + extra + 32 + outputs + groups);
   B200_DISPATCH_DTYPE(dtype, T, launch(route_kernel<T>, dim3(n), dim3(128), smem, stream, static_cast<const T*>(h), wr, br,
-                                       ids, wts, width, experts, top, score));
+                                       ids, wts, width, outputs, top, score, correction, groups, keep, scale, extra, extra_out));
   return launch_status();
+}
+
+extern "C" int b200_moe_route(const void* h, const float* wr, const float* br, int* ids, float* wts, int n, int width, int experts,
+                              int top, int score, int dtype, cudaStream_t stream) {
+  if (score < 0 || score > 1) return B200_ERR_BAD_SIZE;
+  return b200_moe_route_grouped(h, wr, br, nullptr, ids, wts, nullptr, n, width, experts, top, score, 1, 1, 1.f, 0, dtype, stream);
 }
 
 extern "C" int b200_moe_tile_rows() { return b200::BM; }
@@ -473,6 +576,17 @@ extern "C" int b200_gather_rows_bf16(const void* x, const int* sorted_token, voi
   if (rows <= 0) return 0;
   if (width <= 0 || width % 8 != 0) return B200_ERR_BAD_SIZE;
   launch(gather_rows_kernel, dim3(rows), dim3(128), 0, stream, static_cast<const uint4*>(x), sorted_token, static_cast<uint4*>(out), width / 8);
+  return launch_status();
+}
+
+extern "C" int b200_moe_combine_mixed(const float* rows, const int* pair_row, const float* wts, const void* x, const float* extra,
+                                      const float* extra_scale, float* out, int n, int width, int top, int dtype,
+                                      cudaStream_t stream) {
+  using namespace b200;
+  if (n <= 0) return 0;
+  if (width <= 0 || top <= 0 || x == nullptr || wts == nullptr || (extra != nullptr && extra_scale == nullptr)) return B200_ERR_BAD_SIZE;
+  B200_DISPATCH_DTYPE(dtype, T, launch(combine_mixed_kernel<T>, dim3(n), dim3(256), 0, stream, rows, pair_row, wts,
+                                       static_cast<const T*>(x), extra, extra_scale, out, width, top));
   return launch_status();
 }
 

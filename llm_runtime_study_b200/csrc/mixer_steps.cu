@@ -9,13 +9,14 @@ namespace b200 {
 // Rows [q: nq x d | k: nkv x d | v: nkv x dv | ...].  Each q and k head is divided by its root mean
 // square (eps inside the root), times q_w / k_w (d floats each) where given; q goes to q_out
 // [n, nq, d], k and v into the pages [pages, nkv, page_size, d | dv] at the token's position.
-// `normalise` 0 leaves q and k as they are.
+// `normalise` 0 leaves q and k as they are.  The values start at column v_off of the row: (nq + nkv) * d where v has
+// columns of its own; nq * d where the values are the keys as projected (before their norm; dv = d then).
 template <typename T>
 __global__ void __launch_bounds__(128)
 head_norm_write_kernel(const T* __restrict__ rows, int ld, T* __restrict__ q_out, const float* __restrict__ q_w,
                        const float* __restrict__ k_w, float eps, int normalise, const int* __restrict__ positions,
                        const int* __restrict__ token_entry, const int* __restrict__ block_table, int table_stride,
-                       int page_size, T* __restrict__ k_pool, T* __restrict__ v_pool, int nq, int nkv, int d, int dv) {
+                       int page_size, T* __restrict__ k_pool, T* __restrict__ v_pool, int nq, int nkv, int d, int dv, int v_off) {
   pdl_trigger();
   pdl_wait();
   const int token = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
@@ -42,7 +43,7 @@ head_norm_write_kernel(const T* __restrict__ rows, int ld, T* __restrict__ q_out
       w = k_w;
     } else {
       const int h = head - nq - nkv;
-      src = row + (nq + nkv) * d + h * dv;
+      src = row + v_off + h * dv;
       dst = page >= 0 ? v_pool + ((static_cast<size_t>(page) * nkv + h) * page_size + in_page) * dv : nullptr;
       width = dv;
     }
@@ -229,17 +230,29 @@ norm_accumulate_round_kernel(const float* __restrict__ x, const float* __restric
 
 }  // namespace b200
 
+// v_off: the column at which the values' heads start in a row.
+extern "C" int b200_head_norm_write_at(const void* rows, int ld, void* q_out, const float* q_w, const float* k_w, float eps,
+                                       int normalise, const int* positions, const int* token_entry, const int* block_table,
+                                       int table_stride, int page_size, void* k_pool, void* v_pool, int n, int nq, int nkv, int d,
+                                       int dv, int v_off, int dtype, cudaStream_t stream) {
+  using namespace b200;
+  if (n <= 0) return 0;
+  if (nq < 0 || nkv < 0 || nq + nkv <= 0 || d <= 0 || dv <= 0 || page_size <= 0 || ld < (nq + nkv) * d || v_off < 0 ||
+      ld < v_off + nkv * dv)
+    return B200_ERR_BAD_SIZE;
+  B200_DISPATCH_DTYPE(dtype, T, launch(head_norm_write_kernel<T>, dim3(n), dim3(128), 0, stream, static_cast<const T*>(rows), ld,
+                                       static_cast<T*>(q_out), q_w, k_w, eps, normalise, positions, token_entry, block_table,
+                                       table_stride, page_size, static_cast<T*>(k_pool), static_cast<T*>(v_pool), nq, nkv, d, dv,
+                                       v_off));
+  return launch_status();
+}
+
 extern "C" int b200_head_norm_write(const void* rows, int ld, void* q_out, const float* q_w, const float* k_w, float eps,
                                     int normalise, const int* positions, const int* token_entry, const int* block_table,
                                     int table_stride, int page_size, void* k_pool, void* v_pool, int n, int nq, int nkv, int d,
                                     int dv, int dtype, cudaStream_t stream) {
-  using namespace b200;
-  if (n <= 0) return 0;
-  if (nq < 0 || nkv < 0 || nq + nkv <= 0 || d <= 0 || dv <= 0 || page_size <= 0 || ld < nq * d + nkv * (d + dv)) return B200_ERR_BAD_SIZE;
-  B200_DISPATCH_DTYPE(dtype, T, launch(head_norm_write_kernel<T>, dim3(n), dim3(128), 0, stream, static_cast<const T*>(rows), ld,
-                                       static_cast<T*>(q_out), q_w, k_w, eps, normalise, positions, token_entry, block_table,
-                                       table_stride, page_size, static_cast<T*>(k_pool), static_cast<T*>(v_pool), nq, nkv, d, dv));
-  return launch_status();
+  return b200_head_norm_write_at(rows, ld, q_out, q_w, k_w, eps, normalise, positions, token_entry, block_table, table_stride,
+                                 page_size, k_pool, v_pool, n, nq, nkv, d, dv, (nq + nkv) * d, dtype, stream);
 }
 
 extern "C" int b200_latent_prepare(const void* rows, int ld, int q_off, int q_rank, const float* q_w, void* cq_out, int kv_off,

@@ -1,4 +1,4 @@
-from . import mabedra, qwen3, ropulix, sorulix  # registers the architectures
+from . import mabedra, qwen3, ropulix, sorulix, tafisun  # registers the architectures
 from .description import LayerDescription, ModelDescription, tensor_schema
 from .loading import load_model_dir, random_model
 from .model import DecoderModel

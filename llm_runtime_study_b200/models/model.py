@@ -57,6 +57,10 @@ class DecoderModel:
         needs = []
         for layer_index, source in zip(self.order, self.description.cache_of):
             needs.append(None if source is not None else self.blocks[layer_index][1].cache_requirement())
+        # an embedding that keeps something per request (the token before a step's first one) asks behind the last run
+        embedding_need = getattr(self.embedding, "cache_requirement", lambda: None)()
+        if embedding_need is not None:
+            needs.append(embedding_need)
         return CacheLayout.from_requirements(needs)
 
     def bind_cache(self, manager: CacheManager) -> None:
@@ -64,6 +68,7 @@ class DecoderModel:
             manager.layer_cache(run if source is None else source)
             for run, source in enumerate(self.description.cache_of)
         ]
+        self._embedding_cache = manager.layer_cache(len(self.order))
 
     def graph_safe(self) -> bool:
         """Whether every part allows its launches to be replayed from a CUDA graph."""
@@ -84,7 +89,9 @@ class DecoderModel:
         for run in steps:       # a stream step changes the rows before the norm reads them: nothing is prepared for it
             if run > 0:
                 readers[run - 1] = None
-        if getattr(self.embedding, "fuses_norms", False):
+        if getattr(self.embedding, "takes_context", False):      # it reads positions and entries, and may keep state per request
+            first = self.embedding.forward(ctx, self._embedding_cache)
+        elif getattr(self.embedding, "fuses_norms", False):
             first = self.embedding.forward(ctx.token_ids, next_norm=None if 0 in steps else blocks[0].first_norm())
         else:
             first = self.embedding.forward(ctx.token_ids)

@@ -23,9 +23,12 @@ def tensor_core_supported(q: torch.Tensor, cache: Any) -> bool:
 
 
 def paged_attention_rules(q: torch.Tensor, cache: Any, ctx: Any, table: torch.Tensor, *, scale: float, window: int = 0,
-                          softcap: float = 0.0, slopes: torch.Tensor | None = None, sink: bool = False) -> torch.Tensor:
+                          softcap: float = 0.0, slopes: torch.Tensor | None = None, sink: bool = False, chunk: int = 0,
+                          log_bias: "tuple[torch.Tensor, torch.Tensor] | None" = None) -> torch.Tensor:
     """Causal attention of the batch's query tokens ``[N, heads, d]`` over their requests' pages with
-    ``S <- cap * tanh(S / cap)``, ``S <- S - slope_h * distance`` and the sink's ``1 +`` in the denominator.
+    ``S <- cap * tanh(S / cap)``, ``S <- S - slope_h * distance``, ``S <- S - r1_h ln(1 + r2_h * distance)`` (``log_bias = (r1, r2)``),
+    the sink's ``1 +`` in the denominator, and a mask in blocks (``chunk > 0``: a position sees its own block of ``chunk``
+    positions, counted from 0, only).
 
     float32 runtime, and shapes no tensor-core kernel takes (values of another head size than the keys): the
     CUDA-core kernel (one warp per token and head, float32 arithmetic, tiles of 32 keys from key 0, so the order
@@ -34,6 +37,9 @@ def paged_attention_rules(q: torch.Tensor, cache: Any, ctx: Any, table: torch.Te
     kernel with one row tile per CTA (head sizes 64 and 128, portions of 32 tokens and more, no window) or the
     mma.sync kernel; for batches of single decoded tokens the split-sequence mma.sync kernel with its merge."""
 
+    if chunk or log_bias is not None:
+        return _masked(q, cache, ctx, table, scale=scale, window=window, softcap=softcap, slopes=slopes, sink=sink, chunk=chunk,
+                       log_bias=log_bias)
     if BACKEND in ("mma", "tcgen05") and tensor_core_supported(q, cache):
         n, nq, d = q.shape
         keys, values = cache.keys, cache.values
@@ -77,4 +83,14 @@ def paged_attention_rules(q: torch.Tensor, cache: Any, ctx: Any, table: torch.Te
     return F.paged_attention_simt_rules(
         q, cache.keys, cache.values, positions=ctx.positions, token_entry=ctx.token_entry, block_table=table,
         scale=scale, window=window, softcap=softcap, slopes=slopes, sink=sink,
+    )
+
+
+def _masked(q: torch.Tensor, cache: Any, ctx: Any, table: torch.Tensor, *, scale: float, window: int, softcap: float,
+            slopes: torch.Tensor | None, sink: bool, chunk: int, log_bias) -> torch.Tensor:
+    """The forms with a mask in blocks or a bias by the logarithm of the distance."""
+
+    return F.paged_attention_simt_rules(
+        q, cache.keys, cache.values, positions=ctx.positions, token_entry=ctx.token_entry, block_table=table,
+        scale=scale, window=window, softcap=softcap, slopes=slopes, sink=sink, chunk=chunk, log_bias=log_bias,
     )

@@ -211,12 +211,13 @@ def qk_rownorm_write(
 def paged_attention_simt_rules(
     q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, *, positions: torch.Tensor, token_entry: torch.Tensor,
     block_table: torch.Tensor, scale: float, window: int = 0, softcap: float = 0.0, slopes: torch.Tensor | None = None,
-    sink: bool = False,
+    sink: bool = False, chunk: int = 0, log_bias: tuple[torch.Tensor, torch.Tensor] | None = None,
 ) -> torch.Tensor:
     """``paged_attention_simt`` with rules on the scores: ``S <- cap * tanh(S / cap)`` (``softcap > 0``), then
-    ``S <- S - slopes[head] * (p - t)``, and with ``sink`` the weights ``exp(S) / (1 + sum exp(S))``.  Values may
-    have a head size of their own: q ``[N, nq, d]``, keys ``[pages, nkv, page, d]``, values ``[pages, nkv, page, dv]``,
-    result ``[N, nq, dv]``."""
+    ``S <- S - slopes[head] * (p - t)``, ``S <- S - r1[head] * ln(1 + r2[head] * (p - t))`` (``log_bias = (r1, r2)``), and with
+    ``sink`` the weights ``exp(S) / (1 + sum exp(S))``.  ``chunk > 0``: position p sees t only inside its own block of ``chunk``
+    positions (counted from 0).  Values may have a head size of their own: q ``[N, nq, d]``, keys ``[pages, nkv, page, d]``,
+    values ``[pages, nkv, page, dv]``, result ``[N, nq, dv]``."""
 
     require(q, "q", dims=3)
     n, nq, d = q.shape
@@ -231,10 +232,54 @@ def paged_attention_simt_rules(
     require(block_table, "block_table", dtype=torch.int32, dims=2)
     if slopes is not None:
         require(slopes, "slopes", dtype=torch.float32, shape=(nq,))
+    r1 = r2 = None
+    if log_bias is not None:
+        r1, r2 = log_bias
+        require(r1, "log_bias[0]", dtype=torch.float32, shape=(nq,))
+        require(r2, "log_bias[1]", dtype=torch.float32, shape=(nq,))
+    if d > 256 or dv > 256:
+        raise KernelError(f"head sizes {d} and {dv} must be at most 256")
     out = torch.empty((n, nq, dv), dtype=q.dtype, device=q.device)
-    call("b200_paged_attention_simt_rules", ptr(q), ptr(k_pool), ptr(v_pool), ptr(out), ptr(positions), ptr(token_entry),
-         ptr(block_table), block_table.shape[1], page_size, n, nq, nkv, d, dv, float(scale), int(window), float(softcap),
-         ptr(slopes), 1 if sink else 0, tag(q.dtype), stream_ptr())
+    call("b200_paged_attention_simt_masked", ptr(q), ptr(k_pool), ptr(v_pool), ptr(out), ptr(positions), ptr(token_entry),
+         ptr(block_table), block_table.shape[1], page_size, n, nq, nkv, d, dv, dv, float(scale), int(window), float(softcap),
+         ptr(slopes), 1 if sink else 0, int(chunk), ptr(r1), ptr(r2), tag(q.dtype), stream_ptr())
+    return out
+
+
+def relu2(x: torch.Tensor) -> torch.Tensor:
+    """``relu(x)^2`` element by element, in the type of ``x``."""
+
+    require(x, "x")
+    out = torch.empty_like(x)
+    call("b200_relu2", ptr(x), ptr(out), x.numel(), tag(x.dtype), stream_ptr())
+    return out
+
+
+def embedding_sum(ids: torch.Tensor, table: torch.Tensor, bigram: torch.Tensor | None, *, positions: torch.Tensor,
+                  token_entry: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, previous: torch.Tensor | None,
+                  freq: torch.Tensor | None, buckets: int = 0, mul_prev: int = 0, mul_cur: int = 0, scale: float = 1.0) -> torch.Tensor:
+    """``table[id] * scale + bigram[row] + pos(p)`` as float32 rows: ``row = (previous token * mul_prev + id * mul_cur) mod buckets``,
+    row ``buckets`` at position 0; ``pos(p)``: column ``2i`` is ``sin(p * freq[i])``, column ``2i + 1`` the cosine (``freq`` float64).
+    The token before a step's first token of a request is read from ``previous[slot]`` (int32 per request slot), which then
+    receives the entry's last token.  ``bigram`` and ``freq`` may each be ``None``."""
+
+    require(ids, "ids", dtype=torch.int32, dims=1)
+    require(table, "table", dims=2)
+    n, (vocab, hidden) = ids.shape[0], table.shape
+    for t, name in ((positions, "positions"), (token_entry, "token_entry")):
+        require(t, name, dtype=torch.int32, shape=(n,))
+    require(q_start, "q_start", dtype=torch.int32, dims=1)
+    entries = q_start.shape[0] - 1
+    require(slots, "slots", dtype=torch.int32, shape=(entries,))
+    if bigram is not None:
+        require(bigram, "bigram", dtype=table.dtype, shape=(buckets + 1, hidden))
+        require(previous, "previous", dtype=torch.int32)
+    if freq is not None:
+        require(freq, "freq", dtype=torch.float64, shape=((hidden + 1) // 2,))
+    out = torch.empty((n, hidden), dtype=torch.float32, device=ids.device)
+    call("b200_embedding_sum", ptr(ids), ptr(table), ptr(bigram), ptr(out), ptr(positions), ptr(token_entry), ptr(q_start), ptr(slots),
+         ptr(previous), ptr(freq), n, entries, hidden, vocab, int(buckets), int(mul_prev), int(mul_cur), float(scale), tag(table.dtype),
+         stream_ptr(), launches=2 if bigram is not None else 1)
     return out
 
 

@@ -68,6 +68,7 @@ class Routing:
     tile_group: torch.Tensor
     top: int
     tile_rows: int = 64
+    extra: torch.Tensor | None = None      # float32 [N, extra]: sigmoids of the router's further rows (gates for every token)
 
     @property
     def rows(self) -> int:
@@ -78,38 +79,49 @@ def tile_rows() -> int:
     return query("b200_moe_tile_rows")
 
 
-SCORES = {"softmax_chosen": 0, "sigmoid": 1}
+SCORES = {"softmax_chosen": 0, "sigmoid": 1, "softmax_all": 2}
 
 
 def route(h: torch.Tensor, router: torch.Tensor, bias: torch.Tensor | None, *, top: int, wide_tiles: bool = False,
-          score: str = "softmax_chosen") -> Routing:
-    """Logits ``router @ h + bias`` in float32 (``router`` float32 ``[experts, width]``; ``h`` in the activation type), the ``top``
-    largest chosen (the lower index wins a tie); weights by ``score``: the softmax over the chosen logits, or each chosen
-    logit's sigmoid (not renormalised).  Then the pairs sorted by expert, each expert's rows padded to whole tiles (of 128
-    rows with ``wide_tiles``, what the tcgen05 kernel takes; else of 64)."""
+          score: str = "softmax_chosen", correction: torch.Tensor | None = None, groups: int = 1, keep: int = 1,
+          scale: float = 1.0, identity: int = 0, extra: int = 0) -> Routing:
+    """Logits ``router @ h + bias`` in float32 (``router`` float32 ``[outputs + extra, width]``; ``h`` in the activation type), the
+    ``top`` largest chosen (the lower index wins a tie); weights by ``score``: the softmax over the chosen logits, each chosen
+    logit's sigmoid (not renormalised), or (``softmax_all``) the chosen outputs' shares ``s`` of the softmax over all outputs
+    times ``scale``, where the choice goes by ``s + correction`` among the outputs of the ``keep`` best of ``groups`` equal
+    groups of neighbours (a group scores its largest choice score).  The last ``identity`` outputs have no expert behind them
+    (their pairs get no row: ``pair_row`` -1).  ``extra`` further rows of ``router`` give one number per token each, whose
+    sigmoids are returned in ``Routing.extra``.  Then the pairs sorted by expert, each expert's rows padded to whole tiles
+    (of 128 rows with ``wide_tiles``, what the tcgen05 kernel takes; else of 64)."""
 
     require(h, "h", dims=2)
     n, width = h.shape
     require(router, "router", dtype=torch.float32, dims=2)
-    experts = router.shape[0]
+    outputs = router.shape[0] - extra
+    experts = outputs - identity
+    if experts <= 0 or identity < 0 or extra < 0:
+        raise KernelError(f"router of {router.shape[0]} rows does not hold {identity} identity outputs and {extra} further rows")
     if router.shape[1] != width:
         raise KernelError(f"router has shape {tuple(router.shape)}, expected [experts, {width}]")
     if bias is not None:
-        require(bias, "bias", dtype=torch.float32, shape=(experts,))
+        require(bias, "bias", dtype=torch.float32, shape=(outputs + extra,))
+    if correction is not None:
+        require(correction, "correction", dtype=torch.float32, shape=(outputs,))
     dev = h.device
     ids = torch.empty((n, top), dtype=torch.int32, device=dev)
     weights = torch.empty((n, top), dtype=torch.float32, device=dev)
+    extra_out = torch.empty((n, extra), dtype=torch.float32, device=dev) if extra else None
     if score not in SCORES:
         raise KernelError(f"unknown router score {score!r}; expected one of {sorted(SCORES)}")
-    call("b200_moe_route", ptr(h), ptr(router), ptr(bias), ptr(ids), ptr(weights), n, width, experts, top, SCORES[score], tag(h.dtype),
-         stream_ptr())
+    call("b200_moe_route_grouped", ptr(h), ptr(router), ptr(bias), ptr(correction), ptr(ids), ptr(weights), ptr(extra_out), n, width,
+         outputs, top, SCORES[score], int(groups), int(keep), float(scale), int(extra), tag(h.dtype), stream_ptr())
     tile = TC_TILE_ROWS if wide_tiles else tile_rows()
     max_tiles = min(-(-n * top // tile) + experts, n * top)       # a tile holds one expert's rows only
     pair_row = torch.empty(n * top, dtype=torch.int32, device=dev)
     sorted_token = torch.empty(max_tiles * tile, dtype=torch.int32, device=dev)
     tile_group = torch.empty(max_tiles, dtype=torch.int32, device=dev)
     call("b200_moe_plan", ptr(ids), n * top, top, experts, ptr(sorted_token), ptr(pair_row), ptr(tile_group), max_tiles, tile, stream_ptr())
-    return Routing(ids, weights, pair_row, sorted_token, tile_group, top, tile)
+    return Routing(ids, weights, pair_row, sorted_token, tile_group, top, tile, extra_out)
 
 
 def wide_tiles_pay(n: int, top: int, dtype: torch.dtype, *widths: int) -> bool:
@@ -168,4 +180,23 @@ def combine(rows: torch.Tensor, routing: Routing, *, weighted: bool = True) -> t
     out = torch.empty((n, rows.shape[1]), dtype=torch.float32, device=rows.device)
     call("b200_moe_combine", ptr(rows), ptr(routing.pair_row), ptr(routing.weights) if weighted else None, ptr(out), n, rows.shape[1],
          routing.top, stream_ptr())
+    return out
+
+
+def combine_mixed(rows: torch.Tensor, routing: Routing, x: torch.Tensor, *, extra: torch.Tensor | None = None,
+                  extra_scale: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[t] = sum_j weights[t, j] * r_j + extra_scale[t] * extra[t]`` with ``r_j = rows[pair_row[t, j]]``, or ``x[t]`` (the token's
+    own input row, activation type) where the pair has no row (an output that returns its input).  float32, ``j`` ascending."""
+
+    require(rows, "rows", dtype=torch.float32, dims=2)
+    n, width = routing.ids.shape[0], rows.shape[1]
+    require(x, "x", shape=(n, width))
+    if extra is not None:
+        require(extra, "extra", dtype=torch.float32, shape=(n, width))
+        require(extra_scale, "extra_scale", dtype=torch.float32)
+        if extra_scale.numel() != n:
+            raise KernelError("combine_mixed: one factor per token is expected")
+    out = torch.empty((n, width), dtype=torch.float32, device=rows.device)
+    call("b200_moe_combine_mixed", ptr(rows), ptr(routing.pair_row), ptr(routing.weights), ptr(x), ptr(extra), ptr(extra_scale), ptr(out),
+         n, width, routing.top, tag(x.dtype), stream_ptr())
     return out

@@ -27,16 +27,19 @@ def head_norm_write(
     rows: torch.Tensor, *, num_q_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, eps: float,
     q_weight: torch.Tensor | None = None, k_weight: torch.Tensor | None = None, normalise: bool = True,
     positions: torch.Tensor, token_entry: torch.Tensor, block_table: torch.Tensor, page_size: int,
-    k_pool: torch.Tensor, v_pool: torch.Tensor,
+    k_pool: torch.Tensor, v_pool: torch.Tensor, value_offset: int | None = None,
 ) -> torch.Tensor:
     """Rows ``[q | k | v | ...]``: every q and k head divided by its root mean square (``eps`` inside the root), times a
     weight of ``head_dim`` floats where given; q is returned ``[N, nq, d]``, k and v go into the pages
-    ``[pages, nkv, page_size, d | dv]`` at each token's position."""
+    ``[pages, nkv, page_size, d | dv]`` at each token's position.  ``value_offset``: the column at which the values' heads
+    start (default: behind the keys); ``nq * d`` makes the values the keys as projected, before their norm."""
 
     require(rows, "rows", dims=2)
     n, ld = rows.shape
-    if ld < num_q_heads * head_dim + num_kv_heads * (head_dim + value_dim):
-        raise KernelError(f"rows of width {ld} do not hold nq*d + nkv*(d + dv)")
+    if value_offset is None:
+        value_offset = (num_q_heads + num_kv_heads) * head_dim
+    if ld < (num_q_heads + num_kv_heads) * head_dim or value_offset < 0 or ld < value_offset + num_kv_heads * value_dim:
+        raise KernelError(f"rows of width {ld} do not hold nq*d + nkv*d and the values at column {value_offset}")
     dt = rows.dtype
     require(positions, "positions", dtype=torch.int32, shape=(n,))
     require(token_entry, "token_entry", dtype=torch.int32, shape=(n,))
@@ -50,9 +53,9 @@ def head_norm_write(
         raise KernelError(f"pools have shapes {tuple(k_pool.shape)} and {tuple(v_pool.shape)}, expected "
                           f"[pages, {num_kv_heads}, {page_size}, {head_dim} | {value_dim}]")
     q_out = torch.empty((n, num_q_heads, head_dim), dtype=dt, device=rows.device)
-    call("b200_head_norm_write", ptr(rows), ld, ptr(q_out), ptr(q_weight), ptr(k_weight), float(eps), 1 if normalise else 0,
+    call("b200_head_norm_write_at", ptr(rows), ld, ptr(q_out), ptr(q_weight), ptr(k_weight), float(eps), 1 if normalise else 0,
          ptr(positions), ptr(token_entry), ptr(block_table), block_table.shape[1], page_size, ptr(k_pool), ptr(v_pool), n,
-         num_q_heads, num_kv_heads, head_dim, value_dim, tag(dt), stream_ptr())
+         num_q_heads, num_kv_heads, head_dim, value_dim, int(value_offset), tag(dt), stream_ptr())
     return q_out
 
 
@@ -197,4 +200,25 @@ def gated_recurrence(gates: torch.Tensor, u: torch.Tensor, proj: torch.Tensor, *
     call("b200_gated_recurrence", ptr(gates), ptr(u), ptr(proj), proj.shape[1], y_offset, ptr(lam), float(decay_scale), ptr(state),
          ptr(q_start), ptr(slots), ptr(out), ptr(scratch[0]), ptr(scratch[1]), n, entries, width, block_width, tag(u.dtype),
          stream_ptr(), launches=2)
+    return out
+
+
+def mingru_scan(proj: torch.Tensor, *, width: int, z_offset: int, u_offset: int, g_offset: int, state: torch.Tensor,
+                q_start: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
+    """The minGRU recurrence over the rows of one stacked projection (columns ``z_offset``, ``u_offset``, ``g_offset``, each
+    ``width`` wide): ``z = sigmoid(zl)``, candidate ``u + 1/2`` where ``u >= 0`` else ``sigmoid(u)``,
+    ``S_t = (1 - z_t) S_(t-1) + z_t c_t`` continued from ``state[slot]`` (float32 ``[slots, width]``, updated in place), output
+    ``S_t * silu(g_t)`` ``[N, width]`` in the type of ``proj``."""
+
+    require(proj, "proj", dims=2)
+    n, ld = proj.shape
+    require(state, "state", dtype=torch.float32, dims=2)
+    require(q_start, "q_start", dtype=torch.int32, dims=1)
+    entries = q_start.shape[0] - 1
+    require(slots, "slots", dtype=torch.int32, shape=(entries,))
+    if state.shape[1] != width or max(z_offset, u_offset, g_offset) + width > ld:
+        raise KernelError("mingru_scan: the columns lie outside the rows, or the state has another width")
+    out = torch.empty((n, width), dtype=proj.dtype, device=proj.device)
+    call("b200_mingru_scan", ptr(proj), ld, z_offset, u_offset, g_offset, ptr(out), ptr(state), ptr(q_start), ptr(slots), n, entries, width,
+         tag(proj.dtype), stream_ptr())
     return out

@@ -51,7 +51,18 @@ _LIBRARIES = {
             "b200_glu_limit": [c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p],
             "b200_rmsnorm_accumulate": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p],
             "b200_add_rows": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+            "b200_relu2": [c_void_p, c_void_p, c_longlong, c_int, c_void_p],
         },
+    ),
+    "b200_embedding_sum": (
+        ("embedding_sum.cu",),
+        {"b200_embedding_sum": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_float, c_int, c_void_p]},
+    ),
+    "b200_mingru": (
+        ("mingru.cu",),
+        {"b200_mingru_scan": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                              c_void_p]},
     ),
     "b200_gemm_f32": (
         ("gemm_f32.cu",),
@@ -67,6 +78,11 @@ _LIBRARIES = {
             "b200_paged_attention_simt_rules": [
                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                 c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_int, c_int, c_void_p,
+            ],
+            "b200_paged_attention_simt_masked": [
+                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
+                c_void_p,
             ],
             "b200_paged_attention_simt_strided": [
                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
@@ -96,6 +112,8 @@ _LIBRARIES = {
         {
             "b200_head_norm_write": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_void_p,
                                      c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+            "b200_head_norm_write_at": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_void_p,
+                                        c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
             "b200_latent_prepare": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
                                     c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
             "b200_rope_slice": [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
@@ -121,6 +139,10 @@ _LIBRARIES = {
                                   c_void_p, c_longlong, c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                   c_int, c_int, c_int, c_void_p],
             "b200_moe_route": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+            "b200_moe_route_grouped": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                       c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
+            "b200_moe_combine_mixed": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                       c_void_p],
             "b200_moe_tile_rows": [],
             "b200_moe_plan": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
             "b200_gather_rows_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],

@@ -9,6 +9,7 @@ from typing import Any, Mapping
 import torch
 
 from ..ops import attention_latent
+from ..ops import attention_rules
 from ..ops import functional as F
 from ..ops import grouped as G
 from ..ops import mixer_steps as M
@@ -79,6 +80,76 @@ class GatedAttention(Mixer):
         gate_offset = self.num_heads * self.head_dim + self.num_kv_heads * (self.head_dim + self.value_dim)
         gated = M.sigmoid_gate(out.view(out.shape[0], -1), proj, gate_offset=gate_offset, group=self.value_dim)
         return self.o_proj(gated, torch.float32)
+
+
+@MIXERS.register("chunked_attention")
+class ChunkedAttention(Mixer):
+    """Grouped-query causal attention without rotation or value projection: ``q = W_q x``, ``k = W_k x`` (heads of ``head_dim``); the
+    values are the keys as projected; then every q and k head is RMS-normed with one weight of ``head_dim`` numbers for all
+    heads (``q.norm``, ``k.norm``; ``eps`` inside the root).  ``S = scale * q.k - r1_h ln(1 + r2_h (i - j))`` with two numbers per query
+    head (``log_bias``; off: no such term and no ``r1``, ``r2``); position i sees ``j <= i`` in its own block of ``chunk`` positions
+    counted from position 0 (``None``: all before it); ordinary softmax; the heads side by side are multiplied element by
+    element with ``sigmoid(W_g x)``; then ``W_o``.  Query head h reads key/value head ``h // (heads / kv_heads)``.
+
+    The pages hold the normed keys and, as values, the keys before their norm.  Tensors: ``q``, ``k``, ``g`` (one stacked
+    product), ``q.norm``, ``k.norm``, ``r1``, ``r2``, ``o``."""
+
+    graph_safe = True
+
+    def __init__(self, *, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, eps: float, scale: float | None = None,
+                 chunk: int | None = None, log_bias: bool = True) -> None:
+        if min(hidden_size, num_heads, num_kv_heads, head_dim) <= 0:
+            raise ValueError("attention sizes must be positive")
+        if num_heads % num_kv_heads:
+            raise ValueError(f"num_heads {num_heads} is not a multiple of num_kv_heads {num_kv_heads}")
+        if chunk is not None and chunk <= 0:
+            raise ValueError("a chunk must be positive")
+        if head_dim > 256:
+            raise ValueError(f"head size {head_dim} must be at most 256: no kernel takes a larger one")
+        self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = hidden_size, num_heads, num_kv_heads, head_dim
+        self.scale = 1.0 / math.sqrt(head_dim) if scale is None else float(scale)
+        self.eps, self.chunk, self.log_bias = float(eps), chunk, bool(log_bias)
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        h, d = self.hidden_size, self.head_dim
+        specs = {
+            "q": TensorSpec((self.num_heads * d, h)), "k": TensorSpec((self.num_kv_heads * d, h)), "g": TensorSpec((self.num_heads * d, h)),
+            "q.norm": TensorSpec((d,), init="one_plus_normal", std=0.05), "k.norm": TensorSpec((d,), init="one_plus_normal", std=0.05),
+            "o": TensorSpec((h, self.num_heads * d)),
+        }
+        if self.log_bias:
+            specs["r1"] = TensorSpec((self.num_heads,), init="normal", std=0.5)
+            specs["r2"] = TensorSpec((self.num_heads,), init="abs_normal", std=0.5)
+        return specs
+
+    def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
+        self.runtime = runtime
+        self.in_proj = _padded([tensors[n] for n in ("q", "k", "g")], runtime)
+        self.o_proj = Projection([tensors["o"]], None, runtime)
+        self.q_weight = runtime.place_vector_f32(tensors["q.norm"])
+        self.k_weight = runtime.place_vector_f32(tensors["k.norm"])
+        self.bias = (runtime.place_vector_f32(tensors["r1"]), runtime.place_vector_f32(tensors["r2"])) if self.log_bias else None
+
+    def cache_requirement(self) -> PagedTensors:
+        # a block of the mask is never read from behind its end: what lies a whole block back may be given up
+        shape = (self.num_kv_heads, self.head_dim)
+        return PagedTensors(tensors=(("keys", shape), ("values", shape)), window=self.chunk)
+
+    adds_to_residual = True
+    fuses_norms = True
+
+    def forward(self, x: Any, ctx: Any, cache: Any, residual: torch.Tensor | None = None, next_norm: Any = None):
+        proj = self.in_proj(x)                      # [N, q | k | g]
+        table = ctx.block_table(cache.group)
+        nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
+        q = M.head_norm_write(
+            proj, num_q_heads=nq, num_kv_heads=nkv, head_dim=d, value_dim=d, eps=self.eps, q_weight=self.q_weight,
+            k_weight=self.k_weight, positions=ctx.positions, token_entry=ctx.token_entry, block_table=table,
+            page_size=cache.page_size, k_pool=cache.keys, v_pool=cache.values, value_offset=nq * d,
+        )
+        out = attention_rules.paged_attention_rules(q, cache, ctx, table, scale=self.scale, chunk=self.chunk or 0, log_bias=self.bias)
+        gated = M.sigmoid_gate(out.view(out.shape[0], -1), proj, gate_offset=(nq + nkv) * d, group=1)
+        return self.o_proj(gated, torch.float32, add_to=residual, next_norm=next_norm)
 
 
 @MIXERS.register("latent_attention")

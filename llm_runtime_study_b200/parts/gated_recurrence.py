@@ -1,4 +1,4 @@
-"""A mixer that keeps one float32 number per channel and request: a gated linear recurrence behind a short convolution."""
+"""Mixers that keep one float32 number per channel and request: a gated linear recurrence behind a short convolution, and minGRU."""
 
 from __future__ import annotations
 
@@ -74,3 +74,43 @@ class GatedLinearRecurrence(Mixer):
                                  decay_scale=self.decay_scale, state=cache.states["state"], q_start=ctx.q_start, slots=ctx.slots,
                                  block_width=self.block_width)
         return self.o_proj(out, torch.float32)
+
+
+@MIXERS.register("min_gru")
+class MinGRU(Mixer):
+    """A gated recurrence whose gates read the current token only: ``z = sigmoid(W_z x + b_z)``, ``u = W_x x + b_x`` (``width``
+    channels each), candidate ``c = u + 1/2`` where ``u >= 0`` and ``sigmoid(u)`` where ``u < 0``, ``S_t = (1 - z_t) S_(t-1) + z_t c_t``
+    per channel from ``S = 0``; output ``W_o (S_t * silu(W_g x))``.
+
+    Per request: the float32 state ``[width]``.  Tensors: ``z``, ``z.b``, ``x``, ``x.b``, ``g`` (one stacked product), ``o``."""
+
+    graph_safe = True
+
+    def __init__(self, *, hidden_size: int, width: int) -> None:
+        if min(hidden_size, width) <= 0:
+            raise ValueError("recurrence sizes must be positive")
+        self.hidden_size, self.width = hidden_size, width
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        h, w = self.hidden_size, self.width
+        small = dict(init="normal", std=0.5)
+        return {"z": TensorSpec((w, h)), "z.b": TensorSpec((w,), **small), "x": TensorSpec((w, h)), "x.b": TensorSpec((w,), **small),
+                "g": TensorSpec((w, h)), "o": TensorSpec((h, w))}
+
+    def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
+        self.runtime = runtime
+        no_bias = torch.zeros(self.width, dtype=torch.float32)
+        self.in_proj = Projection([tensors["z"], tensors["x"], tensors["g"]], [tensors["z.b"], tensors["x.b"], no_bias], runtime)
+        self.o_proj = Projection([tensors["o"]], None, runtime)
+
+    def cache_requirement(self):
+        return FixedState((self.width,), torch.float32, name="state")
+
+    adds_to_residual = True
+    fuses_norms = True
+
+    def forward(self, x: Any, ctx: Any, cache: Any, residual: torch.Tensor | None = None, next_norm: Any = None):
+        proj = self.in_proj(x)                      # [N, z | u | g]
+        out = M.mingru_scan(proj, width=self.width, z_offset=0, u_offset=self.width, g_offset=2 * self.width,
+                            state=cache.states["state"], q_start=ctx.q_start, slots=ctx.slots)
+        return self.o_proj(out, torch.float32, add_to=residual, next_norm=next_norm)

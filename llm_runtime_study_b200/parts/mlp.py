@@ -91,6 +91,32 @@ class LimitedGLU(FeedForward):
         return self.down_proj(hidden, torch.float32, add_to=residual)
 
 
+@FEED_FORWARDS.register("relu2_mlp")
+class SquaredReluMLP(FeedForward):
+    """``W_down relu(W_up x)^2`` without biases.  Tensors: ``up``, ``down``."""
+
+    graph_safe = True
+
+    def __init__(self, *, hidden_size: int, intermediate_size: int) -> None:
+        if hidden_size <= 0 or intermediate_size <= 0:
+            raise ValueError("relu2_mlp sizes must be positive")
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        return {"up": TensorSpec((self.intermediate_size, self.hidden_size)), "down": TensorSpec((self.hidden_size, self.intermediate_size))}
+
+    def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
+        self.runtime = runtime
+        self.up_proj = Projection([tensors["up"]], None, runtime)
+        self.down_proj = Projection([tensors["down"]], None, runtime)
+
+    adds_to_residual = True
+    fuses_norms = True
+
+    def forward(self, x: Any, ctx: Any, residual: torch.Tensor | None = None, next_norm: Any = None):
+        return self.down_proj(F.relu2(self.up_proj(x)), torch.float32, add_to=residual, next_norm=next_norm)
+
+
 @FEED_FORWARDS.register("poly_norm_mlp")
 class PolyNormMLP(FeedForward):
     """``W_down act(W_up x)`` without biases, ``act(z) = a u(z) + b u(z^2) + c u(z^3) + e`` with element-wise powers and

@@ -32,7 +32,7 @@ class TensorSpec:
     ``kind`` is ``"float"`` (converted to the run type at placement) or ``"int"``
     (index tables; placed as int32).  ``init`` tells
     the random-weights mode how to fill it: ``"normal"`` N(0, std),
-    ``"one_plus_normal"`` 1 + N(0, std), ``"zeros"``.  ``optional`` tensors may
+    ``"one_plus_normal"`` 1 + N(0, std), ``"abs_normal"`` |N(0, std)|, ``"zeros"``.  ``optional`` tensors may
     be absent (a tied output head).
     """
 

@@ -49,6 +49,8 @@ def random_tensor(
         values.normal_(0.0, spec.std, generator=generator)
         if spec.init == "one_plus_normal":
             values += 1.0
+        elif spec.init == "abs_normal":
+            values.abs_()
         elif spec.init != "normal":
             raise ValueError(f"unknown init {spec.init!r} for {name}")
     return values.to(dtype)
