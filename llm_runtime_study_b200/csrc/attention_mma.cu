@@ -18,7 +18,9 @@
 // The prefill kernel and the decode kernel with the query heads on the row side exist a second
 // time with rules on the scores (template RULES): S <- cap * tanh(S / cap), S <- S - slope_h * (p - t)
 // with one slope per query head, and a sink (a key of score 0 without a value, so that the
-// denominator of the softmax gains a 1).  The kernels without rules are unchanged by this.
+// denominator of the softmax gains a 1).  Two more rules of the same kernels: S <- S - r1_h ln(1 + r2_h (p - t)) with two
+// numbers per query head, and a mask in blocks (position p sees t only if floor(p / chunk) = floor(t / chunk), blocks
+// counted from position 0 of the sequence).  The kernels without rules are unchanged by this.
 #include "common.cuh"
 #include "mma.cuh"
 
@@ -53,6 +55,9 @@ struct AttnParams {
   float scale, softcap;            // softcap <= 0: none
   const float* slopes;             // [nq] or null
   int sink;
+  int chunk;                       // > 0: a position sees its own block of `chunk` positions only
+  const float* log_r1;             // [nq] each, or both null: S <- S - r1 ln(1 + r2 (p - t))
+  const float* log_r2;
   // prefill
   const int* tile_entry;
   const int* tile_start;
@@ -107,6 +112,8 @@ struct ScoreRules {
   float scale, softcap, inv_cap;   // scores in natural units: S * scale, then the cap
   float slope[2];                  // of the two rows' query heads
   int pos[2];                      // the two rows' positions (the distance to key t is pos - t)
+  float r1[2], r2[2];              // of the two rows' query heads; log_bias false: no such term
+  bool log_bias;
 };
 
 __device__ __forceinline__ float tanh_exp(float y) {   // 1 - 2 / (e^(2y) + 1): two special-function results
@@ -147,6 +154,7 @@ __device__ __forceinline__ void warp_attend(const bf16* kbuf, const bf16* vbuf, 
         float x = s[nt][e] * rules->scale;
         if (rules->softcap > 0.f) x = rules->softcap * tanh_exp(x * rules->inv_cap);
         x -= rules->slope[i] * static_cast<float>(rules->pos[i] - t);
+        if (rules->log_bias) x -= rules->r1[i] * __logf(fmaf(rules->r2[i], static_cast<float>(rules->pos[i] - t), 1.f));
         s[nt][e] = visible ? x * 1.4426950408889634f : -INFINITY;
       } else {
         s[nt][e] = visible ? s[nt][e] * scale_log2 : -INFINITY;
@@ -234,6 +242,7 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_kernel(AttnParam
     row_ok[i] = tl < ntok && g < p.group;
     row_hi[i] = p_first + tl;
     row_lo[i] = p.window > 0 ? max(0, row_hi[i] - p.window + 1) : 0;
+    if (RULES && p.chunk > 0) row_lo[i] = max(row_lo[i], row_hi[i] / p.chunk * p.chunk);
     row_off[i] = (static_cast<long>(tok0 + tl) * p.nq + kvh * p.group + g) * D;
   }
   ScoreRules rules{};
@@ -247,7 +256,10 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_kernel(AttnParam
       const int g = slice * p.gs + R % p.gs;
       rules.slope[i] = (p.slopes && g < p.group) ? p.slopes[kvh * p.group + g] : 0.f;
       rules.pos[i] = row_hi[i];
+      rules.r1[i] = (p.log_r1 && g < p.group) ? p.log_r1[kvh * p.group + g] : 0.f;
+      rules.r2[i] = (p.log_r1 && g < p.group) ? p.log_r2[kvh * p.group + g] : 0.f;
     }
+    rules.log_bias = p.log_r1 != nullptr;
   }
   uint32_t qf[KSTEPS][4];
   load_q_fragments(qf, p.q, row_off, row_ok);
@@ -259,7 +271,8 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_kernel(AttnParam
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[dt][e] = 0.f;
 
-  const int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0;
+  int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0;
+  if (RULES && p.chunk > 0) lo = max(lo, p_first / p.chunk * p.chunk);      // the first token's block starts earliest
   const int t_begin = (lo / BN) * BN;
   const int ntiles = (p_last - t_begin) / BN + 1;
   load_kv_tile<WARPS * 32>(ks, vs, p, table, kvh, t_begin, lo, p_last);
@@ -306,7 +319,8 @@ __global__ void __launch_bounds__(128) decode_attention_kernel(AttnParams p) {
   const int* table = p.block_table + static_cast<size_t>(b) * p.table_stride;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
   const int len = p.kv_len[b];
-  const int lo = p.window > 0 ? max(0, len - p.window) : 0;
+  int lo = p.window > 0 ? max(0, len - p.window) : 0;
+  if (RULES && p.chunk > 0 && len > 0) lo = max(lo, (len - 1) / p.chunk * p.chunk);
   int chunk = (len - lo + p.num_splits - 1) / p.num_splits;
   chunk = ((chunk + BN - 1) / BN) * BN;
   const int c0 = lo + split * chunk;
@@ -334,7 +348,10 @@ __global__ void __launch_bounds__(128) decode_attention_kernel(AttnParams p) {
       const int g = slice * p.gs + gid + i * 8;
       rules.slope[i] = (p.slopes && row_ok[i]) ? p.slopes[kvh * p.group + g] : 0.f;
       rules.pos[i] = len - 1;
+      rules.r1[i] = (p.log_r1 && row_ok[i]) ? p.log_r1[kvh * p.group + g] : 0.f;
+      rules.r2[i] = (p.log_r1 && row_ok[i]) ? p.log_r2[kvh * p.group + g] : 0.f;
     }
+    rules.log_bias = p.log_r1 != nullptr;
   }
   uint32_t qf[KSTEPS][4];
   load_q_fragments(qf, p.q, row_off, row_ok);
@@ -721,7 +738,8 @@ static int prefill_entry(bool with_rules, const void* q, const void* k_pool, con
                          const int* positions, const int* block_table, int table_stride,
                          int page_size, int nq, int nkv, float scale, int window, float softcap, const float* slopes, int sink,
                          const int* tile_entry, const int* tile_start, const int* tile_count,
-                         int num_tiles, cudaStream_t stream) {
+                         int num_tiles, cudaStream_t stream, int chunk = 0, const float* log_r1 = nullptr,
+                         const float* log_r2 = nullptr) {
   if (num_tiles <= 0) return 0;
   AttnParams p{};
   if (int e = fill_common(p, q, k_pool, v_pool, out, positions, block_table, table_stride, page_size, nq, nkv, scale, window)) return e;
@@ -732,6 +750,10 @@ static int prefill_entry(bool with_rules, const void* q, const void* k_pool, con
   p.softcap = softcap;
   p.slopes = slopes;
   p.sink = sink;
+  p.chunk = chunk;
+  p.log_r1 = log_r1;
+  p.log_r2 = log_r2;
+  if ((log_r1 == nullptr) != (log_r2 == nullptr) || chunk < 0) return B200_ERR_BAD_SIZE;
   dim3 grid(nkv * p.slices, num_tiles);
   if (grid.y > 65535) return B200_ERR_TOO_LARGE;
   if (with_rules) {
@@ -763,6 +785,18 @@ extern "C" int b200_attention_prefill_rules_bf16(const void* q, const void* k_po
                                                  const int* tile_count, int num_tiles, cudaStream_t stream) {
   return prefill_entry(true, q, k_pool, v_pool, out, positions, block_table, table_stride, page_size, nq, nkv, scale, window,
                        softcap, slopes, sink, tile_entry, tile_start, tile_count, num_tiles, stream);
+}
+
+// The same with a mask in blocks (chunk <= 0: none) and the bias by the logarithm of the distance (log_r1, log_r2: [nq]
+// floats each, or both null).
+extern "C" int b200_attention_prefill_masked_bf16(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                                  const int* positions, const int* block_table, int table_stride,
+                                                  int page_size, int nq, int nkv, float scale, int window, float softcap,
+                                                  const float* slopes, int sink, int chunk, const float* log_r1,
+                                                  const float* log_r2, const int* tile_entry, const int* tile_start,
+                                                  const int* tile_count, int num_tiles, cudaStream_t stream) {
+  return prefill_entry(true, q, k_pool, v_pool, out, positions, block_table, table_stride, page_size, nq, nkv, scale, window,
+                       softcap, slopes, sink, tile_entry, tile_start, tile_count, num_tiles, stream, chunk, log_r1, log_r2);
 }
 
 extern "C" long b200_attention_decode_scratch_floats(int requests, int nq, int num_splits) {
@@ -815,12 +849,14 @@ extern "C" int b200_attention_decode_bf16(const void* q, const void* k_pool, con
 
 // One query token per request with rules on the scores (see b200_attention_prefill_rules_bf16); the kernel with the
 // query heads on the row side, the parts merged with the sink added once.
-extern "C" int b200_attention_decode_rules_bf16(const void* q, const void* k_pool, const void* v_pool, void* out,
-                                                const int* kv_len, const int* block_table, int table_stride,
-                                                int page_size, int requests, int nq, int nkv, float scale, int window,
-                                                float softcap, const float* slopes, int sink,
-                                                int num_splits, float* scratch, long scratch_floats, cudaStream_t stream) {
+extern "C" int b200_attention_decode_masked_bf16(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                                 const int* kv_len, const int* block_table, int table_stride,
+                                                 int page_size, int requests, int nq, int nkv, float scale, int window,
+                                                 float softcap, const float* slopes, int sink, int chunk, const float* log_r1,
+                                                 const float* log_r2, int num_splits, float* scratch, long scratch_floats,
+                                                 cudaStream_t stream) {
   if (requests <= 0) return 0;
+  if ((log_r1 == nullptr) != (log_r2 == nullptr) || chunk < 0) return B200_ERR_BAD_SIZE;
   AttnParams p{};
   if (int e = fill_common(p, q, k_pool, v_pool, out, nullptr, block_table, table_stride, page_size, nq, nkv, scale, window)) return e;
   if (num_splits < 1 || requests > 65535) return B200_ERR_BAD_SIZE;
@@ -833,6 +869,9 @@ extern "C" int b200_attention_decode_rules_bf16(const void* q, const void* k_poo
   p.softcap = softcap;
   p.slopes = slopes;
   p.sink = sink;
+  p.chunk = chunk;
+  p.log_r1 = log_r1;
+  p.log_r2 = log_r2;
   static DeviceOnce once;
   if (int e = configure_once(once, decode_attention_kernel<true>, kSmemBytes)) return e;
   dim3 grid(num_splits, nkv * p.slices, requests);
@@ -843,6 +882,16 @@ extern "C" int b200_attention_decode_rules_bf16(const void* q, const void* k_poo
     launch(decode_merge_kernel, dim3(mgrid), dim3(kMergeThreads), 0, stream, p.part_o, p.part_ml, p.out, nq, num_splits, sink);
   }
   return launch_status();
+}
+
+extern "C" int b200_attention_decode_rules_bf16(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                                const int* kv_len, const int* block_table, int table_stride,
+                                                int page_size, int requests, int nq, int nkv, float scale, int window,
+                                                float softcap, const float* slopes, int sink,
+                                                int num_splits, float* scratch, long scratch_floats, cudaStream_t stream) {
+  return b200_attention_decode_masked_bf16(q, k_pool, v_pool, out, kv_len, block_table, table_stride, page_size, requests, nq, nkv,
+                                           scale, window, softcap, slopes, sink, 0, nullptr, nullptr, num_splits, scratch,
+                                           scratch_floats, stream);
 }
 
 // --------------------------------------------------------------------------------------

@@ -28,6 +28,10 @@ _TABLE = {
                                          + [c_void_p] * 3 + [c_int, c_void_p],
     "b200_attention_decode_rules_bf16": [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_int,
                                                           c_int, c_void_p, c_long, c_void_p],
+    "b200_attention_prefill_masked_bf16": [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_int, c_int,
+                                                            c_void_p, c_void_p] + [c_void_p] * 3 + [c_int, c_void_p],
+    "b200_attention_decode_masked_bf16": [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_int,
+                                                           c_int, c_void_p, c_void_p, c_int, c_void_p, c_long, c_void_p],
 }
 
 

@@ -88,8 +88,39 @@ def paged_attention_rules(q: torch.Tensor, cache: Any, ctx: Any, table: torch.Te
 
 def _masked(q: torch.Tensor, cache: Any, ctx: Any, table: torch.Tensor, *, scale: float, window: int, softcap: float,
             slopes: torch.Tensor | None, sink: bool, chunk: int, log_bias) -> torch.Tensor:
-    """The forms with a mask in blocks or a bias by the logarithm of the distance."""
+    """The forms with a mask in blocks or a bias by the logarithm of the distance: the mma.sync kernels with rules (bfloat16,
+    one head size for keys and values that they are built for), the split-sequence kernel for batches of single tokens (a
+    token reads its own block at most, so the parts are sized for the block), else the CUDA-core kernel."""
 
+    r1, r2 = log_bias if log_bias is not None else (None, None)
+    if BACKEND in ("mma", "tcgen05") and tensor_core_supported(q, cache):
+        n, nq, d = q.shape
+        keys, values = cache.keys, cache.values
+        _, _, _, nkv, page_size, gs, slices = attention_bf16._geometry(q, keys)
+        lib = attention_bf16.library_name(d)
+        out = torch.empty_like(q)
+        if ctx.all_decode and n == ctx.num_entries:
+            reach = min(ctx.max_kv_len, chunk) if chunk else ctx.max_kv_len
+            splits = attention_bf16.decode_splits(n, nkv, slices, reach, head_dim=d)
+            floats = native.query("b200_attention_decode_scratch_floats", n, nq, splits, library=lib)
+            scratch = torch.empty(max(floats, 1), dtype=torch.float32, device=q.device)
+            native.call(
+                "b200_attention_decode_masked_bf16", q.data_ptr(), keys.data_ptr(), values.data_ptr(), out.data_ptr(),
+                ctx.kv_len.data_ptr(), table.data_ptr(), table.shape[1], page_size, n, nq, nkv, float(scale), int(window),
+                float(softcap), native.ptr(slopes), 1 if sink else 0, int(chunk), native.ptr(r1), native.ptr(r2), splits,
+                scratch.data_ptr(), floats, native.stream_ptr(), library=lib, launches=2 if splits > 1 else 1)
+            return out
+        maps = ctx.__dict__.setdefault("_tile_maps", {})
+        per_tile = 64 // gs
+        if per_tile not in maps:
+            maps[per_tile] = attention_bf16.tile_map(ctx.q_lens, per_tile, q.device, ctx.kv_lens)
+        tiles, count = maps[per_tile]
+        native.call(
+            "b200_attention_prefill_masked_bf16", q.data_ptr(), keys.data_ptr(), values.data_ptr(), out.data_ptr(),
+            ctx.positions.data_ptr(), table.data_ptr(), table.shape[1], page_size, nq, nkv, float(scale), int(window),
+            float(softcap), native.ptr(slopes), 1 if sink else 0, int(chunk), native.ptr(r1), native.ptr(r2),
+            tiles[0].data_ptr(), tiles[1].data_ptr(), tiles[2].data_ptr(), count, native.stream_ptr(), library=lib)
+        return out
     return F.paged_attention_simt_rules(
         q, cache.keys, cache.values, positions=ctx.positions, token_entry=ctx.token_entry, block_table=table,
         scale=scale, window=window, softcap=softcap, slopes=slopes, sink=sink, chunk=chunk, log_bias=log_bias,

@@ -99,8 +99,13 @@ class MinGRU(Mixer):
 
     def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
         self.runtime = runtime
-        no_bias = torch.zeros(self.width, dtype=torch.float32)
-        self.in_proj = Projection([tensors["z"], tensors["x"], tensors["g"]], [tensors["z.b"], tensors["x.b"], no_bias], runtime)
+        # g has no bias; zero rows bring the number of outputs to a multiple of eight (rows of results then start on 16 bytes)
+        pad = -3 * self.width % 8
+        weights = [tensors["z"], tensors["x"], tensors["g"]]
+        biases = [tensors["z.b"], tensors["x.b"], torch.zeros(self.width + pad, dtype=torch.float32)]
+        if pad:
+            weights.append(torch.zeros((pad, self.hidden_size), dtype=weights[0].dtype))
+        self.in_proj = Projection(weights, biases, runtime)
         self.o_proj = Projection([tensors["o"]], None, runtime)
 
     def cache_requirement(self):

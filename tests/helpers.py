@@ -435,3 +435,102 @@ def make_mabedra_dir(path: Path, config: dict, seed: int, *, torch_dtype: str = 
     (path / "config.json").write_text(json.dumps(config, indent=1), encoding="utf-8")
     write_file(path / "model.safetensors", state)
     return path, state
+
+
+# ----------------------------------------------------------------- Tafisun
+# A: sizes that are no multiples of 16, grouped heads sharing one key/value head, a recurrence wider than the model, blocks
+# of the mask of 5 and 7 positions beside pages of 4, routers with one and with three groups, with and without outputs that
+# return their input, one that uses all of its outputs, a dense feed-forward and a layer without one, a bigram table of 13
+# rows (many pairs collide), multipliers that overflow 32 bits with the vocabulary's ids.
+TAFISUN_A = {
+    "architecture": "Tafisun", "vocab": 211, "width": 64, "norm": {"eps": 1e-5},
+    "embedding": {"bigram": {"buckets": 13, "mul_prev": 40_000_003, "mul_cur": 11}},
+    "layers": [
+        {"type": "attention", "mixer": {"heads": 4, "kv_heads": 1, "dim": 16, "vdim": 16, "mask": {"size": 5}, "scale": 0.3},
+         "mlp": {"kind": "moe", "expert": {"ff": 40, "limit": 1.5},
+                 "router": {"experts": 5, "identity": 1, "top": 2, "scale": 2.5, "groups": {"count": 3, "keep": 2}},
+                 "shared": {"ff": 24, "limit": 0.75}}},
+        {"type": "mingru", "mixer": {"width": 96}, "mlp": None},
+        {"type": "attention", "mixer": {"heads": 2, "kv_heads": 2, "dim": 24, "vdim": 24, "mask": {"size": 7}, "scale": 0.2},
+         "mlp": {"kind": "dense", "ff": 72}},
+        {"type": "mingru", "mixer": {"width": 40},
+         "mlp": {"kind": "moe", "expert": {"ff": 24, "limit": 3.0},
+                 "router": {"experts": 3, "identity": 0, "top": 3, "scale": 1.0, "groups": {"count": 1, "keep": 1}},
+                 "shared": {"ff": 8, "limit": 2.0}}},
+    ],
+}
+# B: one layer of each kind in the other order, as many key/value heads as query heads, a block of the mask that is no
+# power of two and no multiple of the page, more identity outputs than a group holds, a single router output chosen.
+TAFISUN_B = {
+    "architecture": "Tafisun", "vocab": 131, "width": 48, "norm": {"eps": 1e-6},
+    "embedding": {"bigram": {"buckets": 257, "mul_prev": 1, "mul_cur": 0}},
+    "layers": [
+        {"type": "mingru", "mixer": {"width": 48},
+         "mlp": {"kind": "moe", "expert": {"ff": 16, "limit": 2.0},
+                 "router": {"experts": 5, "identity": 3, "top": 1, "scale": 0.7, "groups": {"count": 4, "keep": 1}},
+                 "shared": {"ff": 56, "limit": 4.0}}},
+        {"type": "attention", "mixer": {"heads": 3, "kv_heads": 3, "dim": 32, "vdim": 32, "mask": {"size": 33}, "scale": 0.18},
+         "mlp": {"kind": "dense", "ff": 40}},
+        {"type": "attention", "mixer": {"heads": 1, "kv_heads": 1, "dim": 8, "vdim": 8, "mask": {"size": 2}, "scale": 0.5}, "mlp": None},
+    ],
+}
+# C: sizes in steps of 16 throughout, which is what the tensor-core kernels of the bfloat16 run type take: heads of 32 and 64,
+# blocks of the mask of one page, of three pages and of 20 positions, experts of 64 hidden units.
+TAFISUN_C = {
+    "architecture": "Tafisun", "vocab": 151, "width": 128, "norm": {"eps": 1e-6},
+    "embedding": {"bigram": {"buckets": 97, "mul_prev": 29, "mul_cur": 5}},
+    "layers": [
+        {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 32, "mask": {"size": 16}, "scale": 0.2},
+         "mlp": {"kind": "moe", "expert": {"ff": 64, "limit": 2.0},
+                 "router": {"experts": 6, "identity": 2, "top": 2, "scale": 1.5, "groups": {"count": 4, "keep": 2}},
+                 "shared": {"ff": 64, "limit": 1.0}}},
+        {"type": "mingru", "mixer": {"width": 128}, "mlp": {"kind": "dense", "ff": 256}},
+        {"type": "attention", "mixer": {"heads": 3, "kv_heads": 1, "dim": 64, "vdim": 64, "mask": {"size": 48}, "scale": 0.125},
+         "mlp": {"kind": "moe", "expert": {"ff": 64, "limit": 2.0},
+                 "router": {"experts": 6, "identity": 2, "top": 2, "scale": 1.5, "groups": {"count": 4, "keep": 2}},
+                 "shared": {"ff": 64, "limit": 1.0}}},
+        {"type": "attention", "mixer": {"heads": 10, "kv_heads": 1, "dim": 16, "vdim": 16, "mask": {"size": 20}, "scale": 0.25}, "mlp": None},
+    ],
+}
+# D: a block of the mask longer than every sequence (every key since the first token is read: far keys), heads of 64 with
+# grouped key/value heads, four of twelve outputs in two passes of eight, a recurrence between them.
+TAFISUN_D = {
+    "architecture": "Tafisun", "vocab": 173, "width": 128, "norm": {"eps": 1e-5},
+    "embedding": {"bigram": {"buckets": 1009, "mul_prev": 7, "mul_cur": 31}},
+    "layers": [
+        {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 64, "vdim": 64, "mask": {"size": 4096}, "scale": 0.125},
+         "mlp": {"kind": "moe", "expert": {"ff": 32, "limit": 2.0},
+                 "router": {"experts": 10, "identity": 2, "top": 4, "scale": 1.0, "groups": {"count": 3, "keep": 2}},
+                 "shared": {"ff": 32, "limit": 2.0}}},
+        {"type": "mingru", "mixer": {"width": 160}, "mlp": None},
+        {"type": "attention", "mixer": {"heads": 2, "kv_heads": 1, "dim": 32, "vdim": 32, "mask": {"size": 100}, "scale": 0.2},
+         "mlp": {"kind": "dense", "ff": 64}},
+    ],
+}
+TAFISUN = {"A": (TAFISUN_A, 41, 4), "B": (TAFISUN_B, 42, 16), "C": (TAFISUN_C, 43, 16), "D": (TAFISUN_D, 44, 16)}   # config, seed, page size
+
+
+def make_tafisun_dir(path: Path, config: dict, seed: int, *, torch_dtype: str = "float32", gain: float = 6.0):
+    """Write a Tafisun model folder with random weights; return (path, {name: CPU tensor as stored}).  The matrices are
+    drawn ``gain`` times larger than the framework's default, so that gates and routers are not all alike; the tables of
+    the embedding are drawn of the size of the position vector's entries."""
+
+    from llm_runtime_study_b200.config import TafisunConfig
+    from llm_runtime_study_b200.models.description import tensor_schema
+    from llm_runtime_study_b200.models.tafisun import describe_tafisun
+    from llm_runtime_study_b200.weights.random_init import random_state
+    from llm_runtime_study_b200.weights.safetensors_io import write_file
+
+    schema = tensor_schema(describe_tafisun(TafisunConfig.from_dict(config)))
+    dtype = {"float32": torch.float32, "bfloat16": torch.bfloat16}[torch_dtype]
+    state = random_state(schema, seed, dtype=torch.float32, include_optional=False)
+    for name, tensor in state.items():
+        if name in ("embed", "bigram"):
+            tensor *= 40.0
+        elif tensor.dim() == 2 and not name.endswith((".router", ".sg")):
+            tensor *= gain
+    state = {name: tensor.to(dtype) for name, tensor in state.items()}
+    path.mkdir(parents=True, exist_ok=True)
+    (path / "config.json").write_text(json.dumps(config, indent=1), encoding="utf-8")
+    write_file(path / "model.safetensors", state)
+    return path, state

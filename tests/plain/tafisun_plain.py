@@ -71,9 +71,10 @@ def sinusoid(T: int, width: int, dtype) -> torch.Tensor:
 
 def embed(tokens: list[int], weights: Mapping[str, torch.Tensor], config: Mapping, dtype) -> torch.Tensor:
     x = weights["embed"].to(dtype)[tokens]
-    bigram = config["embedding"]["bigram"]
-    rows = bigram_rows(tokens, buckets=bigram["buckets"], mul_prev=bigram["mul_prev"], mul_cur=bigram["mul_cur"])
-    x = x + weights["bigram"].to(dtype)[rows]
+    bigram = (config.get("embedding") or {}).get("bigram")
+    if bigram:
+        rows = bigram_rows(tokens, buckets=bigram["buckets"], mul_prev=bigram["mul_prev"], mul_cur=bigram["mul_cur"])
+        x = x + weights["bigram"].to(dtype)[rows]
     return x + sinusoid(len(tokens), config["width"], dtype)
 
 
@@ -114,13 +115,15 @@ def attention_mixer(h, w: Mapping[str, torch.Tensor], m: Mapping, eps: float, dt
     """``w``: the mixer's tensors by their short names (``q``, ``k``, ``q.norm``, ``k.norm``, ``r1``, ``r2``, ``g``, ``o``)."""
 
     T = h.shape[0]
-    H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    H, d = m["heads"], m["dim"]
+    G, dv = m.get("kv_heads", H), m.get("vdim", d)
     q = store(h @ w["q"].to(dtype).T).view(T, H, d)
     k = store(h @ w["k"].to(dtype).T).view(T, G, d)
     v = k                                                       # the values are the keys as projected
     qn = store(rms_norm(q, w["q.norm"].to(dtype), eps))
     kn = store(rms_norm(k, w["k.norm"].to(dtype), eps))
-    a = chunked_attention(qn, kn, v.reshape(T, G, dv), scale=m["scale"], size=m["mask"]["size"],
+    size = (m.get("mask") or {}).get("size") or max(T, 1)
+    a = chunked_attention(qn, kn, v.reshape(T, G, dv), scale=m["scale"], size=size,
                           r1=w["r1"].to(dtype), r2=w["r2"].to(dtype))
     gate = sigmoid(store(h @ w["g"].to(dtype).T))
     return store(store(a).reshape(T, H * dv) * gate) @ w["o"].to(dtype).T
@@ -166,8 +169,10 @@ def limited_unit(h, gate_w, up_w, down_w, limit: float, dtype, store) -> torch.T
     return store(g * sigmoid(1.702 * g) * (u + 1.0)) @ down_w.to(dtype).T
 
 
-def route(h, router_w, correction, r: Mapping, dtype) -> tuple[torch.Tensor, torch.Tensor]:
-    """For every token the ids ``[T, top]`` of the chosen router outputs and their weights ``[T, top]``.
+def route(h, router_w, correction, r: Mapping, dtype, margins: list | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """For every token the ids ``[T, top]`` of the chosen router outputs and their weights ``[T, top]``.  ``margins`` (a list)
+    receives ``[T]``: by how much the choice was clear (the last chosen score over the first one left out, the last kept
+    group over the first one dropped; the smaller of the two).
 
     ``s = softmax(W_router h)`` over all outputs; the choice goes by ``s + correction``: outputs form ``groups.count`` equal
     groups of neighbours, a group scores the largest choice score in it, only outputs of the ``groups.keep`` best groups
@@ -183,18 +188,27 @@ def route(h, router_w, correction, r: Mapping, dtype) -> tuple[torch.Tensor, tor
     allowed = torch.zeros(T, count, dtype=torch.bool)
     allowed.scatter_(1, kept, True)
     allowed = allowed[:, :, None].expand(T, count, per).reshape(T, n)
-    ids = torch.topk(choice.masked_fill(~allowed, -math.inf), r["top"], dim=-1).indices
+    masked = choice.masked_fill(~allowed, -math.inf)
+    ids = torch.topk(masked, r["top"], dim=-1).indices
+    if margins is not None:
+        ranked = torch.sort(masked, dim=-1, descending=True).values
+        gap = ranked[:, r["top"] - 1] - ranked[:, r["top"]] if r["top"] < n else torch.full((T,), math.inf, dtype=dtype)
+        groups_ranked = torch.sort(best, dim=-1, descending=True).values
+        if keep_groups < count:
+            gap = torch.minimum(gap, groups_ranked[:, keep_groups - 1] - groups_ranked[:, keep_groups])
+        margins.append(gap)
     return ids, torch.gather(s, 1, ids) * r["scale"]
 
 
-def moe_ff(h, w: Mapping[str, torch.Tensor], mlp: Mapping, dtype, store, router_input=None) -> torch.Tensor:
+def moe_ff(h, w: Mapping[str, torch.Tensor], mlp: Mapping, dtype, store, router_input=None, margins: list | None = None) -> torch.Tensor:
     """``w``: the feed-forward's tensors by their short names.  The last ``router.identity`` router outputs return their
     input; the shared unit runs for every token, times ``sigmoid(W_sg h)`` (one number a token)."""
 
     r = mlp["router"]
     experts = r["experts"]
     rh = h if router_input is None else router_input
-    ids, weights = route(rh, w["router"], w["correction"], r, dtype)
+    r = {"identity": 0, "scale": 1.0, "groups": {"count": 1, "keep": 1}, **r}
+    ids, weights = route(rh, w["router"], w["correction"], r, dtype, margins)
     out = torch.zeros(h.shape[0], w["router"].shape[1], dtype=dtype)
     for t in range(h.shape[0]):
         for e, weight in zip(ids[t].tolist(), weights[t]):
@@ -215,8 +229,9 @@ def sub(weights: Mapping[str, torch.Tensor], prefix: str) -> dict[str, torch.Ten
 
 
 def forward(weights: Mapping[str, torch.Tensor], config: Mapping, tokens: list[int], dtype=torch.float64, *, store=keep,
-            layers_out: list | None = None) -> torch.Tensor:
-    """Logits ``[T, vocab]`` of one sequence.  ``layers_out`` (a list) receives the residual rows after every layer."""
+            layers_out: list | None = None, margins: list | None = None) -> torch.Tensor:
+    """Logits ``[T, vocab]`` of one sequence.  ``layers_out`` (a list) receives the residual rows after every layer,
+    ``margins`` one ``[T]`` tensor per router (see ``route``)."""
 
     eps = config["norm"]["eps"]
     x = embed(tokens, weights, config, dtype)
@@ -233,7 +248,7 @@ def forward(weights: Mapping[str, torch.Tensor], config: Mapping, tokens: list[i
         if mlp:
             h = store(rms_norm(x, weights[f"l{i}.norm2"].to(dtype), eps))
             ff = sub(weights, f"l{i}.mlp")
-            x = x + (dense_ff(h, ff, dtype, store) if mlp["kind"] == "dense" else moe_ff(h, ff, mlp, dtype, store))
+            x = x + (dense_ff(h, ff, dtype, store) if mlp["kind"] == "dense" else moe_ff(h, ff, mlp, dtype, store, margins=margins))
         if layers_out is not None:
             layers_out.append(x.clone())
     x = rms_norm(x, weights["final.norm"].to(dtype), eps)
