@@ -1119,6 +1119,194 @@ def _mabedra_kernels(peak, timed) -> dict:
     return out
 
 
+# ------------------------------------------------------------------------------ Tafisun beside Ropulix and Qwen3
+TAFISUN_EXPERTS, TAFISUN_IDENTITY, TAFISUN_TOP, TAFISUN_GROUPS, TAFISUN_KEEP, TAFISUN_CHUNK = 8, 2, 2, 5, 3, 1024
+
+
+def _tafisun_config(width, ff, heads, kv_heads, d, pairs, vocab) -> dict:
+    """A minGRU layer and a chunked attention layer in turn; the first layer's feed-forward is dense, every other one a
+    mixture: every token uses TAFISUN_TOP of eight experts of ``ff / 4`` hidden units (or of two outputs that return their
+    input) beside a shared unit of ``ff / 4``."""
+
+    moe = {"kind": "moe", "expert": {"ff": ff // 4, "limit": 7.0},
+           "router": {"experts": TAFISUN_EXPERTS, "identity": TAFISUN_IDENTITY, "top": TAFISUN_TOP, "scale": 1.5,
+                      "groups": {"count": TAFISUN_GROUPS, "keep": TAFISUN_KEEP}},
+           "shared": {"ff": ff // 4, "limit": 7.0}}
+    layers = []
+    for pair in range(pairs):
+        layers += [
+            {"type": "mingru", "mixer": {"width": width}, "mlp": {"kind": "dense", "ff": ff} if pair == 0 else moe},
+            {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": d, "vdim": d, "mask": {"size": TAFISUN_CHUNK},
+                                            "scale": d ** -0.5}, "mlp": moe},
+        ]
+    return {"architecture": "Tafisun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "torch_dtype": "bfloat16",
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}}, "layers": layers}
+
+
+def run_tafisun(args) -> dict:
+    """Prefill and decode of Tafisun at layer sizes of real models (random weights), beside Ropulix (the closest design:
+    masked attention beside a recurrence per channel, and experts) and Qwen3 at equal width, heads, head size and depth,
+    through the same engine; then the new kernels alone against the bytes or flops they must move, each beside the like
+    kernel of an existing path."""
+
+    peak, timed, measure = _engine_measurer(args)
+    results = {}
+    for name in (() if args.only == "kernels" else args.size.split(",") if args.size else SORULIX_SIZES):
+        shape = SORULIX_SIZES[name]
+        results[name] = {"shape": dict(zip(("width", "ff", "heads", "kv_heads", "head_dim", "layer_pairs", "vocab"), shape)),
+                         "experts": TAFISUN_EXPERTS, "identity": TAFISUN_IDENTITY, "top": TAFISUN_TOP, "chunk": TAFISUN_CHUNK,
+                         "tafisun": measure(_tafisun_config(*shape), shape[-1])}
+        if args.only not in ("prefill", "decode"):
+            results[name]["ropulix_equal_size"] = measure(_ropulix_config(*shape), shape[-1])
+            results[name]["qwen3_equal_size"] = measure(_qwen3_like(*shape), shape[-1])
+    kernels = _tafisun_kernels(peak, timed) if args.only in ("all", "kernels") else {}
+    return {"workload": "tafisun", "context": CONTEXT, "steps": args.steps, "warmup": max(args.warmup, 3), "dtype": "bfloat16",
+            "data": "synthetic token ids, seeded random weights", "peaks": peak, "models": results, "kernels": kernels}
+
+
+def _tafisun_kernels(peak, timed) -> dict:
+    """Each new kernel alone at the 4k shape (width 4096, 32 heads of 128 over 8 key/value heads), replayed from a CUDA
+    graph, beside the kernel of an existing path that does the like work; fractions are of the measured copy bandwidth
+    for the bytes a kernel must move."""
+
+    import torch
+    from types import SimpleNamespace
+
+    from llm_runtime_study_b200.ops import attention_bf16, attention_rules
+    from llm_runtime_study_b200.ops import block_steps as B
+    from llm_runtime_study_b200.ops import functional as F
+    from llm_runtime_study_b200.ops import grouped as G
+    from llm_runtime_study_b200.ops import mixer_steps as M
+
+    dev = "cuda:0"
+    width, heads, kv_heads, d, ff = 4096, 32, 8, 128, 12288 // 4
+    out = {}
+    cold = timed
+
+    def timed(fn, repeat):
+        fn()
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        graph.replay()
+        return cold(graph.replay, repeat)
+
+    def frac(moved, ms):
+        return round(moved / ms / 1e6 / peak["hbm_gbs"], 3)
+
+    bf = lambda *shape: (0.05 * torch.randn(*shape, device=dev)).bfloat16()
+    ints = lambda values: torch.tensor(values, dtype=torch.int32, device=dev)
+    # the embedding's sum beside the plain table lookup
+    vocab, buckets = 32000, 65521
+    table, bigram = bf(vocab, width), bf(buckets + 1, width)
+    freq = torch.tensor([10000.0 ** (-2.0 * i / width) for i in range(width // 2)], dtype=torch.float64, device=dev)
+    for n, entries in ((2048, 1), (32, 32)):
+        ids = torch.randint(0, vocab, (n,), dtype=torch.int32, device=dev)
+        per = n // entries
+        positions = ints([2048 * (entries > 1) + j for _ in range(entries) for j in range(per)])
+        entry = ints([e for e in range(entries) for _ in range(per)])
+        q_start, slots = ints(list(range(0, n + 1, per))), ints(list(range(entries)))
+        previous = torch.zeros(entries + 1, 1, dtype=torch.int32, device=dev)
+        t_new = timed(lambda: F.embedding_sum(ids, table, bigram, positions=positions, token_entry=entry, q_start=q_start, slots=slots,
+                                              previous=previous, freq=freq, buckets=buckets, mul_prev=31, mul_cur=7), 20)
+        t_old = timed(lambda: F.embedding(ids, table), 20)
+        out[f"embedding_{n}_tokens"] = {"summed_us": round(t_new * 1e3, 1), "table_only_us": round(t_old * 1e3, 1),
+                                        "of_measured_copy": {"summed": frac(n * width * 8, t_new), "table_only": frac(n * width * 6, t_old)}}
+    # minGRU beside the gated linear recurrence's two kernels (gates' arithmetic, chain)
+    for n, entries in ((2048, 1), (8192, 4), (32, 32)):
+        proj = bf(n, 3 * width)
+        state = torch.zeros(entries + 1, width, device=dev)
+        q_start, slots = ints(list(range(0, n + 1, n // entries))), ints(list(range(entries)))
+        t_new = timed(lambda: M.mingru_scan(proj, width=width, z_offset=0, u_offset=width, g_offset=2 * width, state=state, q_start=q_start,
+                                            slots=slots), 5)
+        bw = width // heads
+        proj2, u = bf(n, 2 * width), bf(n, width)
+        gates, lam = torch.randn(n, heads, 2 * bw, device=dev), torch.randn(width, device=dev)
+        t_old = timed(lambda: M.gated_recurrence(gates, u, proj2, y_offset=width, lam=lam, decay_scale=8.0, state=state, q_start=q_start,
+                                                 slots=slots, block_width=bw), 5)
+        out[f"recurrence_{n}_tokens_{entries}_requests"] = {
+            "mingru_us": round(t_new * 1e3, 1), "gated_linear_recurrence_us": round(t_old * 1e3, 1),
+            "of_measured_copy": {"mingru": frac(n * width * 8, t_new), "gated_linear_recurrence": frac(n * width * 14, t_old)}}
+    # attention under the block mask with the logarithmic bias beside the plain attention under a window of equal reach
+    page = PAGE_SIZE
+    r1, r2 = torch.rand(heads, device=dev), torch.rand(heads, device=dev)
+    for seqs, length, new in ((1, 2048, 2048), (4, 2048, 2048), (8, 2048, 1), (32, 2048, 1)):
+        lengths, q_lens = [length] * seqs, [new] * seqs
+        pages = seqs * (length // page)
+        table_ = torch.arange(pages, dtype=torch.int32).view(seqs, -1).to(dev)
+        keys, values = bf(pages, kv_heads, page, d), bf(pages, kv_heads, page, d)
+        q = bf(seqs * new, heads, d)
+        positions = ints([p for m, k in zip(lengths, q_lens) for p in range(m - k, m)])
+        entry = ints([i for i, k in enumerate(q_lens) for _ in range(k)])
+        ctx = SimpleNamespace(positions=positions, token_entry=entry, all_decode=new == 1, num_entries=seqs, q_lens=q_lens, kv_lens=lengths,
+                              max_kv_len=length, max_q_len=new, kv_len=ints(lengths), runtime=None, manager=None)
+        cache = SimpleNamespace(keys=keys, values=values, page_size=page, group=0)
+        t_new = timed(lambda: attention_rules.paged_attention_rules(q, cache, ctx, table_, scale=0.09, chunk=TAFISUN_CHUNK, log_bias=(r1, r2)), 5)
+        ctx2 = SimpleNamespace(**vars(ctx))
+        ctx2.tables = [table_]
+        ctx2.block_table = lambda group: table_
+        t_old = timed(lambda: attention_bf16.try_paged_attention(q, cache, ctx2, table_, scale=0.09, window=TAFISUN_CHUNK), 5)
+        seen = sum(p % TAFISUN_CHUNK + 1 for p in positions.tolist())
+        seen_window = sum(min(p + 1, TAFISUN_CHUNK) for p in positions.tolist())
+        name = f"attention_{'prefill' if new > 1 else 'decode'}_{seqs}x{length}"
+        out[name] = {"chunked_ms": round(t_new, 4), "windowed_ms": round(t_old, 4),
+                     "tflops": {"chunked": round(4.0 * heads * d * seen / t_new / 1e9, 1), "windowed": round(4.0 * heads * d * seen_window / t_old / 1e9, 1)}}
+        if new == 1:
+            moved = seqs * kv_heads * 2 * d * 2
+            out[name]["of_measured_copy"] = {"chunked": frac(moved * (seen // seqs), t_new), "windowed": frac(moved * (seen_window // seqs), t_old)}
+    # the router with groups, a correction, identity outputs and the shared unit's gate beside the plain router; the sums
+    outputs = TAFISUN_EXPERTS + TAFISUN_IDENTITY
+    router, correction = torch.randn(outputs + 1, width, device=dev), torch.randn(outputs, device=dev) * 0.1
+    plain_router = torch.randn(ROPULIX_EXPERTS, width, device=dev)
+    for n in (2048, 8):
+        x = bf(n, width)
+        wide = G.wide_tiles_pay(n, TAFISUN_TOP, x.dtype, width, ff)
+        route_new = lambda: G.route(x, router, None, top=TAFISUN_TOP, wide_tiles=wide, score="softmax_all", correction=correction,
+                                    groups=TAFISUN_GROUPS, keep=TAFISUN_KEEP, scale=1.5, identity=TAFISUN_IDENTITY, extra=1)
+        routing = route_new()
+        routing_old = G.route(x, plain_router, None, top=ROPULIX_TOP, wide_tiles=wide)
+        t_route = timed(route_new, 10)
+        t_route_old = timed(lambda: G.route(x, plain_router, None, top=ROPULIX_TOP, wide_tiles=wide), 10)
+        rows, rows_old = torch.randn(routing.rows, width, device=dev), torch.randn(routing_old.rows, width, device=dev)
+        shared = torch.randn(n, width, device=dev)
+        t_sum = timed(lambda: G.combine_mixed(rows, routing, x, extra=shared, extra_scale=routing.extra), 10)
+        t_sum_old = timed(lambda: G.combine(rows_old, routing_old), 10)
+        gate_up = bf(routing.rows, 2 * ff)
+        t_glu = timed(lambda: F.glu_limit(gate_up, 7.0, 1.702), 10)
+        t_silu = timed(lambda: B.silu_mul_scaled(gate_up), 10)
+        out[f"experts_{n}_tokens"] = {
+            "route_and_sort_us": {"grouped": round(t_route * 1e3, 1), "plain": round(t_route_old * 1e3, 1)},
+            "weighted_sum_us": {"with_identity_and_shared": round(t_sum * 1e3, 1), "plain": round(t_sum_old * 1e3, 1)},
+            "weighted_sum_of_measured_copy": {"with_identity_and_shared": frac(n * width * (4 * TAFISUN_TOP + 4 + 4 + 2), t_sum),
+                                              "plain": frac(n * width * (4 * ROPULIX_TOP + 4), t_sum_old)},
+            "gated_unit_us": {"limited": round(t_glu * 1e3, 1), "silu": round(t_silu * 1e3, 1)},
+            "gated_unit_of_measured_copy": {"limited": frac(routing.rows * ff * 6, t_glu), "silu": frac(routing.rows * ff * 6, t_silu)}}
+    # the per-head norm with weights and the keys written twice, and the element-wise gate; squared relu beside SiLU * up
+    n = 2048
+    rows_ = bf(n, (2 * heads + kv_heads) * d)
+    qw, kw = torch.ones(d, device=dev), torch.ones(d, device=dev)
+    positions, entry = ints(list(range(n))), ints([0] * n)
+    table_ = torch.arange(n // page, dtype=torch.int32).view(1, -1).to(dev)
+    keys, values = bf(n // page, kv_heads, page, d), bf(n // page, kv_heads, page, d)
+    t_norm = timed(lambda: M.head_norm_write(rows_, num_q_heads=heads, num_kv_heads=kv_heads, head_dim=d, value_dim=d, eps=1e-6, q_weight=qw,
+                                             k_weight=kw, positions=positions, token_entry=entry, block_table=table_, page_size=page,
+                                             k_pool=keys, v_pool=values, value_offset=heads * d), 10)
+    attn = bf(n, heads * d)
+    t_gate = timed(lambda: M.sigmoid_gate(attn, rows_, gate_offset=(heads + kv_heads) * d, group=1), 10)
+    hidden = bf(n, 12288)
+    t_relu2 = timed(lambda: F.relu2(hidden), 10)
+    both = bf(n, 2 * 12288)
+    t_silu = timed(lambda: F.silu_mul(both), 10)
+    out["small_steps_2048_tokens"] = {
+        "head_norm_write_us": round(t_norm * 1e3, 1), "head_norm_write_of_measured_copy": frac(n * d * (heads * 4 + kv_heads * 6), t_norm),
+        "sigmoid_gate_us": round(t_gate * 1e3, 1), "sigmoid_gate_of_measured_copy": frac(n * heads * d * 6, t_gate),
+        "relu2_us": round(t_relu2 * 1e3, 1), "relu2_of_measured_copy": frac(n * 12288 * 4, t_relu2),
+        "silu_mul_us": round(t_silu * 1e3, 1), "silu_mul_of_measured_copy": frac(n * 12288 * 6, t_silu)}
+    return out
+
+
 def run_reference(args) -> dict:
     """The unmodified reference from baseline/_ref: its own Qwen3ForCausalLM, paged cache,
     CUDA-graph decode and BatchScheduler, driven through Engine.create_scheduler()."""
@@ -1222,12 +1410,13 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--context", type=int, default=0, help="with --only decode: cached tokens per request (default 2048)")
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (named in config)")
-    parser.add_argument("--workload", choices=("default", "staggered14b", "decode32b", "sorulix", "ropulix", "mabedra"), default="default",
+    parser.add_argument("--workload", choices=("default", "staggered14b", "decode32b", "sorulix", "ropulix", "mabedra", "tafisun"), default="default",
                         help="default: Qwen3-8B decode/prefill; staggered14b, decode32b: the larger configurations (either --impl); "
                              "sorulix: the Sorulix design beside Qwen3 at equal sizes, and its kernels alone; "
                              "ropulix: the Ropulix design beside Sorulix and Qwen3 at equal sizes, and its kernels alone; "
-                             "mabedra: the Mabedra design beside Qwen3 and Ropulix at equal sizes, and its kernels alone")
-    parser.add_argument("--size", default="", help="with --workload sorulix, ropulix or mabedra: sizes to run, with commas (2k, 4k; default both)")
+                             "mabedra: the Mabedra design beside Qwen3 and Ropulix at equal sizes, and its kernels alone; "
+                             "tafisun: the Tafisun design beside Ropulix and Qwen3 at equal sizes, and its kernels alone")
+    parser.add_argument("--size", default="", help="with --workload sorulix, ropulix, mabedra or tafisun: sizes to run, with commas (2k, 4k; default both)")
     parser.add_argument("--only", choices=("all", "decode", "prefill", "kernels", "models"), default="all",
                         help="run only the decode steps or only the prefill (for profiler captures of a small case); "
                              "with --workload sorulix: only the kernels alone, or only the whole models")
@@ -1254,6 +1443,11 @@ def main() -> int:
             result = _unavailable("the reference has no model of this design")
         else:
             result = run_mabedra(args)
+    elif args.workload == "tafisun":
+        if args.impl == "reference":
+            result = _unavailable("the reference has no model of this design")
+        else:
+            result = run_tafisun(args)
     else:
         result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result))

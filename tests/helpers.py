@@ -460,7 +460,8 @@ TAFISUN_A = {
     ],
 }
 # B: one layer of each kind in the other order, as many key/value heads as query heads, a block of the mask that is no
-# power of two and no multiple of the page, more identity outputs than a group holds, a single router output chosen.
+# power of two and no multiple of the page, more identity outputs than a group holds, a single router output chosen, no
+# shared unit.
 TAFISUN_B = {
     "architecture": "Tafisun", "vocab": 131, "width": 48, "norm": {"eps": 1e-6},
     "embedding": {"bigram": {"buckets": 257, "mul_prev": 1, "mul_cur": 0}},
@@ -468,7 +469,7 @@ TAFISUN_B = {
         {"type": "mingru", "mixer": {"width": 48},
          "mlp": {"kind": "moe", "expert": {"ff": 16, "limit": 2.0},
                  "router": {"experts": 5, "identity": 3, "top": 1, "scale": 0.7, "groups": {"count": 4, "keep": 1}},
-                 "shared": {"ff": 56, "limit": 4.0}}},
+                 "shared": None}},
         {"type": "attention", "mixer": {"heads": 3, "kv_heads": 3, "dim": 32, "vdim": 32, "mask": {"size": 33}, "scale": 0.18},
          "mlp": {"kind": "dense", "ff": 40}},
         {"type": "attention", "mixer": {"heads": 1, "kv_heads": 1, "dim": 8, "vdim": 8, "mask": {"size": 2}, "scale": 0.5}, "mlp": None},
