@@ -1219,15 +1219,20 @@ def _tafisun_kernels(peak, timed) -> dict:
         proj = bf(n, 3 * width)
         state = torch.zeros(entries + 1, width, device=dev)
         q_start, slots = ints(list(range(0, n + 1, n // entries))), ints(list(range(entries)))
-        t_new = timed(lambda: M.mingru_scan(proj, width=width, z_offset=0, u_offset=width, g_offset=2 * width, state=state, q_start=q_start,
-                                            slots=slots), 5)
+        t_chain = timed(lambda: M.mingru_scan(proj, width=width, z_offset=0, u_offset=width, g_offset=2 * width, state=state, q_start=q_start,
+                                              slots=slots), 5)
+        t_new = t_chain
+        if n // entries >= M.MINGRU_SEGMENT_MIN > 0:      # the form the model runs for portions of this length
+            segments = M.mingru_segment_map([n // entries] * entries, list(range(entries)), dev)
+            t_new = timed(lambda: M.mingru_scan(proj, width=width, z_offset=0, u_offset=width, g_offset=2 * width, state=state,
+                                                q_start=q_start, slots=slots, segments=segments), 5)
         bw = width // heads
         proj2, u = bf(n, 2 * width), bf(n, width)
         gates, lam = torch.randn(n, heads, 2 * bw, device=dev), torch.randn(width, device=dev)
         t_old = timed(lambda: M.gated_recurrence(gates, u, proj2, y_offset=width, lam=lam, decay_scale=8.0, state=state, q_start=q_start,
                                                  slots=slots, block_width=bw), 5)
         out[f"recurrence_{n}_tokens_{entries}_requests"] = {
-            "mingru_us": round(t_new * 1e3, 1), "gated_linear_recurrence_us": round(t_old * 1e3, 1),
+            "mingru_us": round(t_new * 1e3, 1), "mingru_one_chain_us": round(t_chain * 1e3, 1), "gated_linear_recurrence_us": round(t_old * 1e3, 1),
             "of_measured_copy": {"mingru": frac(n * width * 8, t_new), "gated_linear_recurrence": frac(n * width * 14, t_old)}}
     # attention under the block mask with the logarithmic bias beside the plain attention under a window of equal reach
     page = PAGE_SIZE

@@ -10,17 +10,17 @@
 //            last digits already).
 //
 // The token before a step's first token of a request is not in the batch: it is kept per request slot (`previous`,
-// [slots] int32) and replaced, by a second small kernel that runs behind the first, with the step's last token of
-// every entry.  Either table may be left out (null).
+// [slots] int32).  Only the CTA of an entry's first token reads it; the same CTA replaces it, behind a barrier, with the
+// entry's last token of this step, so one launch does both.  Either table may be left out (null).
 #include "common.cuh"
 
 namespace b200 {
 
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(512)
 embedding_sum_kernel(const int* __restrict__ ids, const T* __restrict__ table, const T* __restrict__ bigram, float* __restrict__ out,
                      const int* __restrict__ positions, const int* __restrict__ token_entry, const int* __restrict__ q_start,
-                     const int* __restrict__ slots, const int* __restrict__ previous, const double* __restrict__ freq, int hidden,
+                     const int* __restrict__ slots, int* __restrict__ previous, const double* __restrict__ freq, int hidden,
                      int vocab, int buckets, long long mul_prev, long long mul_cur, float scale) {
   pdl_trigger();
   pdl_wait();
@@ -31,14 +31,19 @@ embedding_sum_kernel(const int* __restrict__ ids, const T* __restrict__ table, c
   const T* erow = table + static_cast<size_t>(id) * hidden;
   const T* brow = nullptr;
   if (bigram != nullptr) {
+    const int entry = token_entry[token];
+    const int first = q_start[entry];
     long long row = buckets;
     if (p > 0) {
-      const int entry = token_entry[token];
-      int before = token > q_start[entry] ? ids[token - 1] : previous[slots[entry]];
+      int before = token > first ? ids[token - 1] : previous[slots[entry]];
       before = min(max(before, 0), vocab - 1);
       row = (static_cast<long long>(before) * mul_prev + static_cast<long long>(id) * mul_cur) % buckets;
     }
     brow = bigram + static_cast<size_t>(row) * hidden;
+    if (token == first) {                   // every thread of this CTA has read the kept token: now it may be replaced
+      __syncthreads();
+      if (threadIdx.x == 0) previous[slots[entry]] = ids[q_start[entry + 1] - 1];
+    }
   }
   float* dst = out + static_cast<size_t>(token) * hidden;
   for (int pair = threadIdx.x; 2 * pair < hidden; pair += blockDim.x) {
@@ -56,18 +61,6 @@ embedding_sum_kernel(const int* __restrict__ ids, const T* __restrict__ table, c
   }
 }
 
-// previous[slot of entry] = the entry's last token of this step
-__global__ void __launch_bounds__(128)
-previous_token_kernel(const int* __restrict__ ids, const int* __restrict__ q_start, const int* __restrict__ slots,
-                      int* __restrict__ previous, int entries) {
-  pdl_trigger();
-  pdl_wait();
-  const int entry = blockIdx.x * blockDim.x + threadIdx.x;
-  if (entry >= entries) return;
-  const int last = q_start[entry + 1] - 1;
-  if (last >= q_start[entry]) previous[slots[entry]] = ids[last];
-}
-
 }  // namespace b200
 
 // ids, positions, token_entry [n]; q_start [entries + 1]; slots [entries]; previous [slots] (null with bigram null);
@@ -80,12 +73,10 @@ extern "C" int b200_embedding_sum(const int* ids, const void* table, const void*
   using namespace b200;
   if (n <= 0) return 0;
   if (hidden <= 0 || vocab <= 0 || entries <= 0 || (bigram != nullptr && (buckets <= 0 || previous == nullptr))) return B200_ERR_BAD_SIZE;
-  B200_DISPATCH_DTYPE(dtype, T, launch(embedding_sum_kernel<T>, dim3(n), dim3(128), 0, stream, ids, static_cast<const T*>(table),
+  const int pairs = (hidden + 1) / 2;
+  const int threads = pairs >= 512 ? 512 : (pairs + 31) / 32 * 32;      // a pair of columns a thread and pass
+  B200_DISPATCH_DTYPE(dtype, T, launch(embedding_sum_kernel<T>, dim3(n), dim3(threads), 0, stream, ids, static_cast<const T*>(table),
                                        static_cast<const T*>(bigram), out, positions, token_entry, q_start, slots, previous, freq,
                                        hidden, vocab, buckets, mul_prev, mul_cur, scale));
-  if (int e = launch_status()) return e;
-  if (bigram != nullptr) {
-    launch(previous_token_kernel, dim3((entries + 127) / 128), dim3(128), 0, stream, ids, q_start, slots, previous, entries);
-  }
   return launch_status();
 }

@@ -279,7 +279,7 @@ def embedding_sum(ids: torch.Tensor, table: torch.Tensor, bigram: torch.Tensor |
     out = torch.empty((n, hidden), dtype=torch.float32, device=ids.device)
     call("b200_embedding_sum", ptr(ids), ptr(table), ptr(bigram), ptr(out), ptr(positions), ptr(token_entry), ptr(q_start), ptr(slots),
          ptr(previous), ptr(freq), n, entries, hidden, vocab, int(buckets), int(mul_prev), int(mul_cur), float(scale), tag(table.dtype),
-         stream_ptr(), launches=2 if bigram is not None else 1)
+         stream_ptr())
     return out
 
 

@@ -4,12 +4,14 @@ behind a short convolution.  Statistics, angles, gates and states are float32 in
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from dataclasses import dataclass
 
 from ..errors import KernelError
-from .native import call, ptr, require, stream_ptr, tag
+from .native import call, ptr, query, require, stream_ptr, tag
 
 
 @dataclass
@@ -203,12 +205,35 @@ def gated_recurrence(gates: torch.Tensor, u: torch.Tensor, proj: torch.Tensor, *
     return out
 
 
+# Longest portion of a step from which the minGRU scan runs in segments (three launches over all segments and channels
+# instead of one chain per request and channel); LLM_RUNTIME_STUDY_B200_MINGRU_SEGMENTS=0: never.
+MINGRU_SEGMENT_MIN = int(os.environ.get("LLM_RUNTIME_STUDY_B200_MINGRU_SEGMENTS", "128"))
+
+
+def mingru_segment_map(q_lens, slots, device) -> tuple[torch.Tensor, int]:
+    """Every entry cut into segments of tokens for ``mingru_scan``: one int32 tensor holding ``seg_first``, ``seg_count``,
+    ``seg_slot`` (``[segments]`` each; the slot for an entry's last segment, else -1) and ``entry_seg`` (``[entries + 1]``)."""
+
+    size = query("b200_mingru_segment_tokens")
+    first, count, slot, entry_seg, at = [], [], [], [0], 0
+    for n, s in zip(q_lens, slots):
+        for start in range(0, n, size):
+            first.append(at + start)
+            count.append(min(size, n - start))
+            slot.append(s if start + size >= n else -1)
+        entry_seg.append(len(first))
+        at += n
+    packed = torch.tensor(first + count + slot + entry_seg, dtype=torch.int32)
+    return packed.to(device), len(first)
+
+
 def mingru_scan(proj: torch.Tensor, *, width: int, z_offset: int, u_offset: int, g_offset: int, state: torch.Tensor,
-                q_start: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
+                q_start: torch.Tensor, slots: torch.Tensor, segments: "tuple[torch.Tensor, int] | None" = None) -> torch.Tensor:
     """The minGRU recurrence over the rows of one stacked projection (columns ``z_offset``, ``u_offset``, ``g_offset``, each
     ``width`` wide): ``z = sigmoid(zl)``, candidate ``u + 1/2`` where ``u >= 0`` else ``sigmoid(u)``,
     ``S_t = (1 - z_t) S_(t-1) + z_t c_t`` continued from ``state[slot]`` (float32 ``[slots, width]``, updated in place), output
-    ``S_t * silu(g_t)`` ``[N, width]`` in the type of ``proj``."""
+    ``S_t * silu(g_t)`` ``[N, width]`` in the type of ``proj``.  ``segments`` (from ``mingru_segment_map``): the form in three
+    launches for long portions, whose results differ from the chain's by rounding."""
 
     require(proj, "proj", dims=2)
     n, ld = proj.shape
@@ -219,6 +244,14 @@ def mingru_scan(proj: torch.Tensor, *, width: int, z_offset: int, u_offset: int,
     if state.shape[1] != width or max(z_offset, u_offset, g_offset) + width > ld:
         raise KernelError("mingru_scan: the columns lie outside the rows, or the state has another width")
     out = torch.empty((n, width), dtype=proj.dtype, device=proj.device)
+    if segments is not None:
+        packed, count = segments
+        require(packed, "segments", dtype=torch.int32, shape=(3 * count + entries + 1,))
+        scratch = torch.empty((2, count, width), dtype=torch.float32, device=proj.device)
+        base, step = packed.data_ptr(), 4 * count
+        call("b200_mingru_scan_segments", ptr(proj), ld, z_offset, u_offset, g_offset, ptr(out), ptr(state), ptr(slots), base, base + step,
+             base + 2 * step, base + 3 * step, ptr(scratch), n, entries, count, width, tag(proj.dtype), stream_ptr(), launches=3)
+        return out
     call("b200_mingru_scan", ptr(proj), ld, z_offset, u_offset, g_offset, ptr(out), ptr(state), ptr(q_start), ptr(slots), n, entries, width,
          tag(proj.dtype), stream_ptr())
     return out

@@ -62,7 +62,10 @@ _LIBRARIES = {
     "b200_mingru": (
         ("mingru.cu",),
         {"b200_mingru_scan": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                              c_void_p]},
+                              c_void_p],
+         "b200_mingru_segment_tokens": [],
+         "b200_mingru_scan_segments": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]},
     ),
     "b200_gemm_f32": (
         ("gemm_f32.cu",),

@@ -116,6 +116,15 @@ class MinGRU(Mixer):
 
     def forward(self, x: Any, ctx: Any, cache: Any, residual: torch.Tensor | None = None, next_norm: Any = None):
         proj = self.in_proj(x)                      # [N, z | u | g]
+        segments = None
+        # long portions in bfloat16: the scan in segments (its sums are grouped by segment, which the 32-bit path, whose
+        # bits do not depend on the cut, must not do); the map is made once a step and shared by the layers
+        if (proj.dtype == torch.bfloat16 and not getattr(ctx, "captured", False) and ctx.entry_slots is not None
+                and 0 < M.MINGRU_SEGMENT_MIN <= ctx.max_q_len):
+            maps = ctx.__dict__.setdefault("_segment_maps", {})
+            if "mingru" not in maps:
+                maps["mingru"] = M.mingru_segment_map(ctx.q_lens, ctx.entry_slots, proj.device)
+            segments = maps["mingru"]
         out = M.mingru_scan(proj, width=self.width, z_offset=0, u_offset=self.width, g_offset=2 * self.width,
-                            state=cache.states["state"], q_start=ctx.q_start, slots=ctx.slots)
+                            state=cache.states["state"], q_start=ctx.q_start, slots=ctx.slots, segments=segments)
         return self.o_proj(out, torch.float32, add_to=residual, next_norm=next_norm)

@@ -321,6 +321,41 @@ def test_mingru_across_cuts(dtype, width, cuts):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width,q_lens", [(40, [300, 1, 33]), (130, [32, 64, 31]), (7, [1, 1]), (96, [1000])])
+def test_mingru_in_segments(dtype, width, q_lens):
+    """The form in three launches for long portions: several requests of unequal length in one batch, each continued from
+    a state of its own, segments that end with the portion, with a full segment and with one token."""
+
+    from llm_runtime_study_b200.ops import mixer_steps as M
+
+    torch.manual_seed(width + len(q_lens))
+    n = sum(q_lens)
+    proj = (2 * torch.randn(n, 3 * width)).to(dtype)
+    slot_of = [3, 0, 2][: len(q_lens)]
+    start = torch.randn(5, width)
+    state = dev(start.clone())
+    q_start = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32)
+    segments = M.mingru_segment_map(q_lens, slot_of, DEV)
+    out = M.mingru_scan(dev(proj), width=width, z_offset=0, u_offset=width, g_offset=2 * width, state=state, q_start=dev(q_start),
+                        slots=dev(torch.tensor(slot_of, dtype=torch.int32)), segments=segments).cpu().double()
+    at = 0
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    for m, slot in zip(q_lens, slot_of):
+        x = proj[at:at + m].double()
+        z, c = plain.sigmoid(x[:, :width]), plain.mingru_candidate(x[:, width:2 * width])
+        S, rows = start[slot].double(), []
+        for t in range(m):
+            S = (1.0 - z[t]) * S + z[t] * c[t]
+            rows.append(S * plain.silu(x[t, 2 * width:]))
+        want = torch.stack(rows)
+        assert (out[at:at + m] - want).abs().max() <= tol * max(1.0, float(want.abs().max())), (slot, m)
+        assert (state[slot].cpu().double() - S).abs().max() < 2e-5 * max(1.0, float(S.abs().max()))
+        at += m
+    untouched = [s for s in range(5) if s not in slot_of]
+    assert torch.equal(state[untouched].cpu(), start[untouched])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("experts,identity,top,groups,keep,width", [(5, 1, 2, 3, 2, 64), (3, 0, 3, 1, 1, 40), (5, 3, 1, 4, 1, 48), (10, 2, 4, 3, 2, 128),
                                                                   (34, 6, 5, 8, 3, 36), (6, 2, 2, 4, 2, 128)])
 def test_the_router_with_groups_a_correction_identity_outputs_and_a_gate(dtype, experts, identity, top, groups, keep, width):
