@@ -316,7 +316,8 @@ def test_mingru_across_cuts(dtype, width, cuts):
         tol = 2e-5 if dtype == torch.float32 else 2e-2
         assert (out[1:] - want[at:at + n]).abs().max() <= tol * max(1.0, float(want.abs().max())), (i, at)
         at += n
-    assert (state[1].cpu().double() - S[-1]).abs().max() < 2e-5
+    # the bfloat16 run type forms its sigmoids with the fast exponential: a few units in the last place of a float32 a step
+    assert (state[1].cpu().double() - S[-1]).abs().max() < (2e-5 if dtype == torch.float32 else 2e-4) * max(1.0, float(S[-1].abs().max()))
     assert (state[0] == 7.0).all() and (state[2] == -3.0).all()
 
 
@@ -349,7 +350,7 @@ def test_mingru_in_segments(dtype, width, q_lens):
             rows.append(S * plain.silu(x[t, 2 * width:]))
         want = torch.stack(rows)
         assert (out[at:at + m] - want).abs().max() <= tol * max(1.0, float(want.abs().max())), (slot, m)
-        assert (state[slot].cpu().double() - S).abs().max() < 2e-5 * max(1.0, float(S.abs().max()))
+        assert (state[slot].cpu().double() - S).abs().max() < (2e-5 if dtype == torch.float32 else 2e-4) * max(1.0, float(S.abs().max()))
         at += m
     untouched = [s for s in range(5) if s not in slot_of]
     assert torch.equal(state[untouched].cpu(), start[untouched])
