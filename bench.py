@@ -1129,7 +1129,7 @@ def _tafisun_config(width, ff, heads, kv_heads, d, pairs, vocab) -> dict:
     input) beside a shared unit of ``ff / 4``."""
 
     moe = {"kind": "moe", "expert": {"ff": ff // 4, "limit": 7.0},
-           "router": {"experts": TAFISUN_EXPERTS, "identity": TAFISUN_IDENTITY, "top": TAFISUN_TOP, "scale": 1.5,
+           "router": {"experts": TAFISUN_EXPERTS, "identity": TAFISUN_IDENTITY, "top": TAFISUN_TOP, "scale": 2.0,
                       "groups": {"count": TAFISUN_GROUPS, "keep": TAFISUN_KEEP}},
            "shared": {"ff": ff // 4, "limit": 7.0}}
     layers = []
@@ -1140,7 +1140,7 @@ def _tafisun_config(width, ff, heads, kv_heads, d, pairs, vocab) -> dict:
                                             "scale": d ** -0.5}, "mlp": moe},
         ]
     return {"architecture": "Tafisun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "torch_dtype": "bfloat16",
-            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}}, "layers": layers}
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 131, "mul_cur": 17}}, "layers": layers}
 
 
 def run_tafisun(args) -> dict:
@@ -1210,7 +1210,7 @@ def _tafisun_kernels(peak, timed) -> dict:
         q_start, slots = ints(list(range(0, n + 1, per))), ints(list(range(entries)))
         previous = torch.zeros(entries + 1, 1, dtype=torch.int32, device=dev)
         t_new = timed(lambda: F.embedding_sum(ids, table, bigram, positions=positions, token_entry=entry, q_start=q_start, slots=slots,
-                                              previous=previous, freq=freq, buckets=buckets, mul_prev=31, mul_cur=7), 20)
+                                              previous=previous, freq=freq, buckets=buckets, mul_prev=131, mul_cur=17), 20)
         t_old = timed(lambda: F.embedding(ids, table), 20)
         out[f"embedding_{n}_tokens"] = {"summed_us": round(t_new * 1e3, 1), "table_only_us": round(t_old * 1e3, 1),
                                         "of_measured_copy": {"summed": frac(n * width * 8, t_new), "table_only": frac(n * width * 6, t_old)}}
@@ -1269,7 +1269,7 @@ def _tafisun_kernels(peak, timed) -> dict:
         x = bf(n, width)
         wide = G.wide_tiles_pay(n, TAFISUN_TOP, x.dtype, width, ff)
         route_new = lambda: G.route(x, router, None, top=TAFISUN_TOP, wide_tiles=wide, score="softmax_all", correction=correction,
-                                    groups=TAFISUN_GROUPS, keep=TAFISUN_KEEP, scale=1.5, identity=TAFISUN_IDENTITY, extra=1)
+                                    groups=TAFISUN_GROUPS, keep=TAFISUN_KEEP, scale=2.0, identity=TAFISUN_IDENTITY, extra=1)
         routing = route_new()
         routing_old = G.route(x, plain_router, None, top=ROPULIX_TOP, wide_tiles=wide)
         t_route = timed(route_new, 10)

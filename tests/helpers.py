@@ -482,14 +482,14 @@ TAFISUN_C = {
     "embedding": {"bigram": {"buckets": 97, "mul_prev": 29, "mul_cur": 5}},
     "layers": [
         {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 32, "mask": {"size": 16}, "scale": 0.2},
-         "mlp": {"kind": "moe", "expert": {"ff": 64, "limit": 2.0},
-                 "router": {"experts": 6, "identity": 2, "top": 2, "scale": 1.5, "groups": {"count": 4, "keep": 2}},
-                 "shared": {"ff": 64, "limit": 1.0}}},
+         "mlp": {"kind": "moe", "expert": {"ff": 64, "limit": 2.5},
+                 "router": {"experts": 6, "identity": 2, "top": 2, "scale": 1.25, "groups": {"count": 4, "keep": 2}},
+                 "shared": {"ff": 64, "limit": 1.5}}},
         {"type": "mingru", "mixer": {"width": 128}, "mlp": {"kind": "dense", "ff": 256}},
         {"type": "attention", "mixer": {"heads": 3, "kv_heads": 1, "dim": 64, "vdim": 64, "mask": {"size": 48}, "scale": 0.125},
-         "mlp": {"kind": "moe", "expert": {"ff": 64, "limit": 2.0},
-                 "router": {"experts": 6, "identity": 2, "top": 2, "scale": 1.5, "groups": {"count": 4, "keep": 2}},
-                 "shared": {"ff": 64, "limit": 1.0}}},
+         "mlp": {"kind": "moe", "expert": {"ff": 64, "limit": 2.5},
+                 "router": {"experts": 6, "identity": 2, "top": 2, "scale": 1.25, "groups": {"count": 4, "keep": 2}},
+                 "shared": {"ff": 64, "limit": 1.5}}},
         {"type": "attention", "mixer": {"heads": 10, "kv_heads": 1, "dim": 16, "vdim": 16, "mask": {"size": 20}, "scale": 0.25}, "mlp": None},
     ],
 }
@@ -497,7 +497,7 @@ TAFISUN_C = {
 # grouped key/value heads, four of twelve outputs in two passes of eight, a recurrence between them.
 TAFISUN_D = {
     "architecture": "Tafisun", "vocab": 173, "width": 128, "norm": {"eps": 1e-5},
-    "embedding": {"bigram": {"buckets": 1009, "mul_prev": 7, "mul_cur": 31}},
+    "embedding": {"bigram": {"buckets": 1009, "mul_prev": 5, "mul_cur": 29}},
     "layers": [
         {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 64, "vdim": 64, "mask": {"size": 4096}, "scale": 0.125},
          "mlp": {"kind": "moe", "expert": {"ff": 32, "limit": 2.0},

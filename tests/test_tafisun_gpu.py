@@ -143,7 +143,7 @@ def _attention_case(dtype, nq, nkv, d, page, lengths, seed):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("nq,nkv,d,page,chunk", [(4, 2, 16, 4, 6), (3, 3, 12, 16, 16), (2, 1, 40, 8, 5), (6, 2, 64, 16, 64), (1, 1, 8, 4, 1)])
+@pytest.mark.parametrize("nq,nkv,d,page,chunk", [(4, 2, 16, 4, 6), (3, 3, 12, 16, 16), (2, 1, 40, 8, 5), (8, 2, 64, 16, 32), (1, 1, 8, 4, 1)])
 def test_head_norm_with_weights_values_from_keys_and_chunked_attention(dtype, nq, nkv, d, page, chunk):
     """The per-head norm with one weight for all heads, the raw keys written as values, and attention under the mask in
     blocks with the bias by the logarithm of the distance, for two sequences in one batch."""
@@ -237,7 +237,7 @@ def test_a_key_at_a_blocks_edge_and_a_far_key(kernel, page, chunk, marked, new):
             assert (row - 3.0).abs().min() > 1.5, (p, row[0, :3])
 
 
-@pytest.mark.parametrize("nq,nkv,d,page,chunk", [(4, 2, 32, 16, 16), (6, 2, 64, 16, 64), (3, 1, 64, 16, 48), (10, 1, 16, 16, 20), (20, 1, 32, 8, 200),
+@pytest.mark.parametrize("nq,nkv,d,page,chunk", [(4, 2, 32, 16, 16), (8, 4, 64, 16, 64), (3, 1, 64, 16, 48), (10, 1, 16, 16, 20), (20, 1, 32, 8, 200),
                                                  (2, 2, 128, 16, 33)])
 @pytest.mark.parametrize("q_lens", [[150, 41], [1, 1], [2, 37], [70, 1]])
 def test_tensor_core_chunked_attention(nq, nkv, d, page, chunk, q_lens):
