@@ -257,56 +257,82 @@ int launch_grouped_mma(const GroupedArgs& g, int batch, int act, cudaStream_t st
 // best groups can be chosen (the lower index wins a tie, as everywhere); weights = s (without the correction) * scale.
 // The router's matrix may hold `extra` further rows behind those of the outputs (one number per token each: a gate on
 // something that runs for every token); their logits' sigmoids go to extra_out [n, extra] and take no part in the choice.
-template <typename T>
+// A CTA takes TOK tokens (batches of many tokens: the router's rows are fetched once for all of them); a token's sums are
+// formed in the same order whatever TOK is, so its logits carry the same bits in every batch.  Warp w then chooses for the
+// CTA's token w.
+template <typename T, int TOK>
 __global__ void __launch_bounds__(128)
 route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ br, int* __restrict__ ids,
-             float* __restrict__ wts, int width, int outputs, int top, int score, const float* __restrict__ correction, int groups,
+             float* __restrict__ wts, int n, int width, int outputs, int top, int score, const float* __restrict__ correction, int groups,
              int keep, float scale, int extra, float* __restrict__ extra_out) {
-  extern __shared__ float logits[];          // [experts], then [4][8] partial sums, then [outputs] probabilities, [groups] scores
+  // per token: [experts] logits, [outputs] probabilities, [groups] scores; then [TOK][4][8] partial sums
+  extern __shared__ float route_smem[];
   const int experts = outputs + extra;       // rows of the router's matrix
-  float* part = logits + experts;
-  float* probs = part + 32;
-  float* group_score = probs + outputs;
+  const int per_token = experts + outputs + groups;
+  float* part = route_smem + TOK * per_token;
   pdl_trigger();
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int token = blockIdx.x;
-  const T* row = h + static_cast<size_t>(token) * width;
-  for (int e0 = 0; e0 < experts; e0 += 8) {
-    float dot[8];
+  const int token0 = blockIdx.x * TOK;
+  const T* rows[TOK];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) dot[j] = 0.f;
+  for (int k = 0; k < TOK; ++k) rows[k] = h + static_cast<size_t>(min(token0 + k, n - 1)) * width;
+  for (int e0 = 0; e0 < experts; e0 += 8) {
+    float dot[TOK][8];
+#pragma unroll
+    for (int k = 0; k < TOK; ++k)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dot[k][j] = 0.f;
     if ((width & 3) == 0) {          // four columns a thread and pass: 16-byte loads of the router's rows
       for (int i = threadIdx.x * 4; i < width; i += 512) {
-        const float x0 = to_float(row[i]), x1 = to_float(row[i + 1]), x2 = to_float(row[i + 2]), x3 = to_float(row[i + 3]);
+        float x[TOK][4];
+#pragma unroll
+        for (int k = 0; k < TOK; ++k)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) x[k][c] = to_float(rows[k][i + c]);
 #pragma unroll
         for (int j = 0; j < 8; ++j)
           if (e0 + j < experts) {
             const float4 w4 = *reinterpret_cast<const float4*>(wr + static_cast<size_t>(e0 + j) * width + i);
-            dot[j] = fmaf(x3, w4.w, fmaf(x2, w4.z, fmaf(x1, w4.y, fmaf(x0, w4.x, dot[j]))));
+#pragma unroll
+            for (int k = 0; k < TOK; ++k)
+              dot[k][j] = fmaf(x[k][3], w4.w, fmaf(x[k][2], w4.z, fmaf(x[k][1], w4.y, fmaf(x[k][0], w4.x, dot[k][j]))));
           }
       }
     } else {
       for (int i = threadIdx.x; i < width; i += 128) {
-        const float x = to_float(row[i]);
+        float x[TOK];
+#pragma unroll
+        for (int k = 0; k < TOK; ++k) x[k] = to_float(rows[k][i]);
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-          if (e0 + j < experts) dot[j] = fmaf(x, wr[static_cast<size_t>(e0 + j) * width + i], dot[j]);
+          if (e0 + j < experts) {
+            const float w = wr[static_cast<size_t>(e0 + j) * width + i];
+#pragma unroll
+            for (int k = 0; k < TOK; ++k) dot[k][j] = fmaf(x[k], w, dot[k][j]);
+          }
       }
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float sum = warp_sum(dot[j]);
-      if (lane == 0) part[warp * 8 + j] = sum;
-    }
+    for (int k = 0; k < TOK; ++k)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float sum = warp_sum(dot[k][j]);
+        if (lane == 0) part[(k * 4 + warp) * 8 + j] = sum;
+      }
     __syncthreads();
-    if (threadIdx.x < 8 && e0 + threadIdx.x < experts) {
-      const int j = threadIdx.x;
-      logits[e0 + j] = ((part[j] + part[8 + j]) + part[16 + j]) + part[24 + j] + (br ? br[e0 + j] : 0.f);
+    if (threadIdx.x < TOK * 8 && e0 + (threadIdx.x & 7) < experts) {
+      const int k = threadIdx.x >> 3, j = threadIdx.x & 7;
+      const float* p = part + k * 32;
+      route_smem[k * per_token + e0 + j] = ((p[j] + p[8 + j]) + p[16 + j]) + p[24 + j] + (br ? br[e0 + j] : 0.f);
     }
     __syncthreads();
   }
-  if (warp != 0) return;
+  if (warp >= TOK || token0 + warp >= n) return;
+  const int token = token0 + warp;
+  float* logits = route_smem + warp * per_token;
+  float* probs = logits + experts;
+  float* group_score = probs + outputs;
   if (lane < extra) extra_out[static_cast<size_t>(token) * extra + lane] = 1.f / (1.f + expf(-logits[outputs + lane]));
   if (score == 2) {
     float mx = -INFINITY;
@@ -545,9 +571,17 @@ extern "C" int b200_moe_route_grouped(const void* h, const float* wr, const floa
       (extra > 0 && extra_out == nullptr) || groups <= 0 || outputs % groups != 0 || keep <= 0 || keep > groups ||
       top > keep * (outputs / groups) || score < 0 || score > 2 || (groups > 1 && score != 2))
     return B200_ERR_BAD_SIZE;
-  const size_t smem = sizeof(float) * (outputs + extra + 32 + outputs + groups);
-  B200_DISPATCH_DTYPE(dtype, T, launch(route_kernel<T>, dim3(n), dim3(128), smem, stream, static_cast<const T*>(h), wr, br,
-                                       ids, wts, width, outputs, top, score, correction, groups, keep, scale, extra, extra_out));
+  // many tokens: four a CTA, one choosing warp each (the router's rows cross the L2 a quarter as often)
+  const bool four = n >= 512;
+  const int tok = four ? 4 : 1;
+  const size_t smem = sizeof(float) * tok * (outputs + extra + outputs + groups + 32);
+  if (smem > 48 * 1024) return B200_ERR_TOO_LARGE;
+  B200_DISPATCH_DTYPE(dtype, T, {
+    if (four) launch(route_kernel<T, 4>, dim3((n + 3) / 4), dim3(128), smem, stream, static_cast<const T*>(h), wr, br, ids, wts, n, width,
+                     outputs, top, score, correction, groups, keep, scale, extra, extra_out);
+    else launch(route_kernel<T, 1>, dim3(n), dim3(128), smem, stream, static_cast<const T*>(h), wr, br, ids, wts, n, width, outputs, top,
+                score, correction, groups, keep, scale, extra, extra_out);
+  });
   return launch_status();
 }
 
