@@ -61,13 +61,42 @@ def _configuration(case: int):
     return raw, lengths, rng
 
 
+# Sizes that no kernel's vector width divides: a width of 100 and of 63, heads of 20 and of 7 columns, hidden sizes of 9, 31 and
+# 50, a recurrence of 33 channels, 48 router outputs in six groups of which six are used, a layer without a mask.
+ODD = {
+    "width-100": ({"architecture": "Tafisun", "vocab": 333, "width": 100, "norm": {"eps": 1e-5},
+                   "embedding": {"bigram": {"buckets": 50, "mul_prev": 3, "mul_cur": 2}},
+                   "layers": [
+                       {"type": "attention", "mixer": {"heads": 3, "kv_heads": 1, "dim": 20, "vdim": 20, "mask": {"size": 10}, "scale": 0.2},
+                        "mlp": {"kind": "moe", "expert": {"ff": 20, "limit": 2.0},
+                                "router": {"experts": 3, "identity": 1, "top": 2, "scale": 1.0, "groups": {"count": 2, "keep": 1}},
+                                "shared": {"ff": 36, "limit": 1.0}}},
+                       {"type": "mingru", "mixer": {"width": 50}, "mlp": {"kind": "dense", "ff": 50}},
+                       {"type": "attention", "mixer": {"heads": 2, "dim": 16, "vdim": 16, "scale": 0.25}, "mlp": None}]},
+                  [1, 2, 33, 130, 65]),
+    "width-63": ({"architecture": "Tafisun", "vocab": 97, "width": 63, "norm": {"eps": 1e-6},
+                  "embedding": {"bigram": {"buckets": 5, "mul_prev": 1, "mul_cur": 1}},
+                  "layers": [
+                      {"type": "mingru", "mixer": {"width": 33},
+                       "mlp": {"kind": "moe", "expert": {"ff": 9, "limit": 2.0},
+                               "router": {"experts": 40, "identity": 8, "top": 6, "scale": 3, "groups": {"count": 6, "keep": 2}},
+                               "shared": {"ff": 7, "limit": 1}}},
+                      {"type": "attention", "mixer": {"heads": 4, "kv_heads": 4, "dim": 7, "vdim": 7, "mask": {"size": 300}, "scale": 1},
+                       "mlp": {"kind": "dense", "ff": 31}}]},
+                 [5, 64, 200, 1, 17]),
+}
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("case", [1, 2, 3, 4, 5, 6, 7, 8, 9, 10])
+@pytest.mark.parametrize("case", [1, 2, 3, 4, 5, 6, 7, 8, 9, 10, "width-100", "width-63"])
 def test_random_configuration(case, dtype, tmp_path):
     from llm_runtime_study_b200.engine.replay import TraceReplayer
     from llm_runtime_study_b200.engine.runtime import load
 
-    raw, lengths, rng = _configuration(case)
+    if isinstance(case, str):
+        (raw, lengths), rng, case = ODD[case], random.Random(len(case)), len(case)
+    else:
+        raw, lengths, rng = _configuration(case)
     path, weights = helpers.make_tafisun_dir(tmp_path / "model", raw, case, torch_dtype=dtype)
     requests = {f"r{i}": helpers.random_tokens(rng, raw["vocab"], n) for i, n in enumerate(lengths)}
     store = plain.round_bfloat16 if dtype == "bfloat16" else plain.keep
